@@ -1,0 +1,88 @@
+/*
+ * Entry points this library adds next to the upstream xnor_nn interface. None of them changes
+ * the six upstream signatures in xnor_nn.h; a program that never includes this header behaves
+ * exactly as it would against upstream, only on the GPU.
+ *
+ * Each declaration names the upstream code whose role it takes over, where there is one.
+ */
+#ifndef XNOR_NN_B200_H
+#define XNOR_NN_B200_H
+
+#include <stdint.h>
+
+#include "xnor_nn.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Kernel family that consumes the packed operands. Upstream picks between its int16 and int32
+ * word paths and its per-ISA kernels inside xnor_nn_init_convolution
+ * (src/implementation.cpp:16-24, src/bcast_convolution.cpp:92-117); this is the same decision
+ * for the GPU. `auto` honours the environment variable XNOR_NN_B200_KERNEL
+ * (popc | mma_b1 | tcgen05_i8) and otherwise picks by shape. */
+typedef enum {
+    xnor_nn_b200_kernel_auto = -1,
+    xnor_nn_b200_kernel_popc = 0,       /* LOP3+POPC integer pipe; every shape and format     */
+    xnor_nn_b200_kernel_mma_b1 = 1,     /* mma.sync m16n8k256 xor.popc; unit stride           */
+    xnor_nn_b200_kernel_tcgen05_i8 = 2  /* tcgen05.mma kind::i8 on +-1 bytes; unit stride     */
+} xnor_nn_b200_kernel_t;
+
+/* xnor_nn_init_convolution (src/common_convolution.cpp:9-63) with the kernel family stated.
+ * A family that cannot serve the shape (strided convolutions on the tensor-core families)
+ * degrades to popc, the way an upstream bcast request degrades to the reference algorithm
+ * when oc is not a multiple of the vector width (src/bcast_convolution.cpp:45-56). */
+xnor_nn_status_t xnor_nn_b200_init_convolution(xnor_nn_convolution_t *c,
+                                               const xnor_nn_algorithm_t algorithm,
+                                               const xnor_nn_tensor_format_t src_fmt,
+                                               const xnor_nn_tensor_format_t weights_fmt,
+                                               const xnor_nn_tensor_format_t dst_fmt,
+                                               int mb, int oc, int ic, int ih, int iw,
+                                               int kh, int kw, int sh, int sw, int ph, int pw,
+                                               xnor_nn_b200_kernel_t kernel);
+
+/* The family the descriptor ended up with. */
+xnor_nn_b200_kernel_t xnor_nn_b200_kernel_of(const xnor_nn_convolution_t *c);
+
+/* One call for what xnor_nn::Convolution::forward does with three (include/xnor_nn.hpp:45-53):
+ * binarize_data, calculate_k and forward on res[user_src] -> res[user_dst]. The source crosses
+ * to the device once instead of twice, and the mean-|x| map is produced by the packing pass. */
+xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_resources_t res);
+
+/* The convolution of the `forward` executor (src/default/bcast_convolution_default.cpp:60-91)
+ * stopped before the alpha*K scaling: writes the signed agreement counts
+ * S = 2*popcount(xnor) - op_c as int32, NCHW, mb*oc*oh*ow entries, to `sums` (host or device
+ * memory). Needs binarize_weights and binarize_data to have run on `res`. This is what the
+ * bit-exact parity tests compare. */
+xnor_nn_status_t xnor_nn_b200_forward_sums(const xnor_nn_convolution_t *c,
+                                           xnor_nn_resources_t res, int32_t *sums);
+
+/* Copies `bytes` of internal slot `slot` (3..8) to host memory. Upstream's internal slots are
+ * host arrays that tests read directly (test/gtest/test_data_bin_reference.cpp:106-121); here
+ * they live on the device, so this is how a test looks at alpha, A, K and the packed words. */
+xnor_nn_status_t xnor_nn_b200_read_resource(const xnor_nn_convolution_t *c,
+                                            xnor_nn_resources_t res, int slot, void *host_dst,
+                                            size_t bytes);
+
+/* Work for `res` is issued on one CUDA stream, by default one the library creates. A framework
+ * that owns the tensors hands in its own stream (a cudaStream_t) so that the kernels order
+ * with its work; NULL goes back to the library's stream. No upstream counterpart: upstream is
+ * synchronous host code. */
+xnor_nn_status_t xnor_nn_b200_set_stream(xnor_nn_resources_t res, void *cuda_stream);
+void *xnor_nn_b200_get_stream(xnor_nn_resources_t res);
+
+/* Blocks until everything issued for `res` has finished. Calls that were given host pointers
+ * have already waited; this is for callers that pass device pointers. */
+xnor_nn_status_t xnor_nn_b200_synchronize(xnor_nn_resources_t res);
+
+/* Text of the most recent CUDA failure seen by the calling thread ("" if none). Upstream
+ * reports through the status code alone (src/status.cpp:3-15). */
+const char *xnor_nn_b200_last_error(void);
+
+/* Number of kernels this library has launched in this process, for benchmark accounting. */
+long xnor_nn_b200_kernel_launches(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XNOR_NN_B200_H */

@@ -1,0 +1,528 @@
+// The C interface: descriptor set-up, device resources, the four executors and the extension
+// entry points. Everything a caller can reach is in this file; kernels are in the neighbours.
+//
+// Host pointers in the user slots are staged through device buffers owned by the resource
+// context and the call returns once the host-visible effect is complete; device pointers are
+// used in place and the call only enqueues work on the context's stream.
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <unordered_map>
+
+#include <cuda_runtime.h>
+
+#include "xnor_nn.h"
+#include "xnor_nn_b200.h"
+
+#include "kernels.cuh"
+#include "plan.hpp"
+
+using namespace xb200;
+
+namespace xb200 {
+std::atomic<long> g_kernel_launches{0};
+}
+
+namespace {
+
+thread_local char t_last_error[256] = "";
+
+bool verbose() {
+    static const bool v = [] {
+        const char *e = getenv("XNOR_NN_VERBOSE");
+        return e && e[0] == '1';
+    }();
+    return v;
+}
+
+xnor_nn_status_t fail(cudaError_t e, const char *what) {
+    snprintf(t_last_error, sizeof t_last_error, "%s: %s", what, cudaGetErrorString(e));
+    if (verbose()) printf("xnor_nn_b200: error: %s\n", t_last_error);
+    (void)cudaGetLastError();  // clear the sticky-less error so later calls start clean
+    if (e == cudaErrorMemoryAllocation) return xnor_nn_error_memory;
+    return xnor_nn_unimplemented;
+}
+
+#define CU(call)                                          \
+    do {                                                  \
+        cudaError_t e__ = (call);                         \
+        if (e__ != cudaSuccess) return fail(e__, #call);  \
+    } while (0)
+
+// Per-resource device context: the stream the work runs on and the staging buffers used when
+// the caller's tensors live in host memory. Found through the alpha slot's device pointer.
+struct ResCtx {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    void *stage[3] = {nullptr, nullptr, nullptr};  // src, weights, dst
+    size_t stage_bytes[3] = {0, 0, 0};
+    int32_t *sums_stage = nullptr;
+    size_t sums_bytes = 0;
+};
+
+std::mutex g_mu;
+std::unordered_map<const void *, ResCtx *> g_ctx;
+
+ResCtx *find_ctx(xnor_nn_resources_t res) {
+    if (!res || !res[xnor_nn_resource_alpha]) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_ctx.find(res[xnor_nn_resource_alpha]);
+    return it == g_ctx.end() ? nullptr : it->second;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+bool on_device(const void *p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+xnor_nn_status_t ensure_stage(ResCtx *x, int which, size_t bytes) {
+    if (x->stage_bytes[which] >= bytes) return xnor_nn_success;
+    if (x->stage[which]) CU(cudaFree(x->stage[which]));
+    x->stage[which] = nullptr;
+    x->stage_bytes[which] = 0;
+    CU(cudaMalloc(&x->stage[which], bytes));
+    x->stage_bytes[which] = bytes;
+    return xnor_nn_success;
+}
+
+// Device view of a read-only user tensor: the pointer itself, or a staged copy.
+xnor_nn_status_t stage_in(ResCtx *x, int which, const void *user, size_t bytes,
+                          const void **dev, bool *staged) {
+    if (on_device(user)) {
+        *dev = user;
+        return xnor_nn_success;
+    }
+    xnor_nn_status_t st = ensure_stage(x, which, bytes);
+    if (st != xnor_nn_success) return st;
+    CU(cudaMemcpyAsync(x->stage[which], user, bytes, cudaMemcpyHostToDevice, x->stream));
+    *dev = x->stage[which];
+    *staged = true;
+    return xnor_nn_success;
+}
+
+const Plan *plan_of(const xnor_nn_convolution_t *c) {
+    return c ? static_cast<const Plan *>(c->state) : nullptr;
+}
+
+size_t src_bytes(const Plan &p) { return (size_t)p.mb * p.ic * p.ih * p.iw * sizeof(float); }
+size_t w_bytes(const Plan &p) { return (size_t)p.oc * p.ic * p.kh * p.kw * sizeof(float); }
+size_t dst_elems(const Plan &p) { return (size_t)p.mb * p.oc * p.oh * p.ow; }
+
+void log_exec(const Plan &p, const char *what) {
+    if (!verbose()) return;
+    printf("xnor_nn_b200: exec: %s: kernel=%s mb=%d ic=%d ih=%d iw=%d oc=%d oh=%d ow=%d "
+           "kh=%d kw=%d sh=%d sw=%d ph=%d pw=%d\n",
+           what, family_name(p.family), p.mb, p.ic, p.ih, p.iw, p.oc, p.oh, p.ow, p.kh, p.kw,
+           p.sh, p.sw, p.ph, p.pw);
+}
+
+// ---- the four executors ------------------------------------------------------------------------
+
+// Replaces upstream src/bcast_binarize_weights.cpp:13-145.
+xnor_nn_status_t exec_binarize_weights(const xnor_nn_convolution_t *c, xnor_nn_resources_t res) {
+    if (!c || !res || !res[xnor_nn_resource_user_weights] || !res[xnor_nn_resource_bin_weights] ||
+        !res[xnor_nn_resource_operations_count] || !res[xnor_nn_resource_alpha])
+        return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x) return xnor_nn_error_invalid_input;
+    if (!p->formats_ok) return xnor_nn_unimplemented;
+    DeviceGuard dg(x->device);
+    log_exec(*p, "binarize_weights");
+    const void *w = nullptr;
+    bool staged = false;
+    xnor_nn_status_t st =
+        stage_in(x, 1, res[xnor_nn_resource_user_weights], w_bytes(*p), &w, &staged);
+    if (st != xnor_nn_success) return st;
+    CU(launch_binarize_weights(*p, (const float *)w, res[xnor_nn_resource_bin_weights],
+                               (float *)res[xnor_nn_resource_alpha],
+                               (int32_t *)res[xnor_nn_resource_operations_count], x->stream));
+    if (staged) CU(cudaStreamSynchronize(x->stream));
+    return xnor_nn_success;
+}
+
+// Replaces upstream src/bcast_binarize_data.cpp:13-76.
+xnor_nn_status_t exec_binarize_data(const xnor_nn_convolution_t *c, xnor_nn_resources_t res) {
+    if (!c || !res || !res[xnor_nn_resource_user_src] || !res[xnor_nn_resource_bin_src])
+        return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x) return xnor_nn_error_invalid_input;
+    if (!p->formats_ok) return xnor_nn_unimplemented;
+    DeviceGuard dg(x->device);
+    log_exec(*p, "binarize_data");
+    const void *src = nullptr;
+    bool staged = false;
+    xnor_nn_status_t st = stage_in(x, 0, res[xnor_nn_resource_user_src], src_bytes(*p), &src, &staged);
+    if (st != xnor_nn_success) return st;
+    CU(launch_binarize_data(*p, (const float *)src, res[xnor_nn_resource_bin_src], nullptr,
+                            x->stream));
+    if (staged) CU(cudaStreamSynchronize(x->stream));
+    return xnor_nn_success;
+}
+
+// Replaces upstream src/bcast_calculate_k.cpp:13-88.
+xnor_nn_status_t exec_calculate_k(const xnor_nn_convolution_t *c, xnor_nn_resources_t res) {
+    if (!c || !res || !res[xnor_nn_resource_user_src] || !res[xnor_nn_resource_a] ||
+        !res[xnor_nn_resource_k])
+        return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x) return xnor_nn_error_invalid_input;
+    if (!p->formats_ok) return xnor_nn_unimplemented;
+    DeviceGuard dg(x->device);
+    log_exec(*p, "calculate_k");
+    const void *src = nullptr;
+    bool staged = false;
+    xnor_nn_status_t st = stage_in(x, 0, res[xnor_nn_resource_user_src], src_bytes(*p), &src, &staged);
+    if (st != xnor_nn_success) return st;
+    CU(launch_mean_abs(*p, (const float *)src, (float *)res[xnor_nn_resource_a], x->stream));
+    CU(launch_box_filter(*p, (const float *)res[xnor_nn_resource_a],
+                         (float *)res[xnor_nn_resource_k], x->stream));
+    if (staged) CU(cudaStreamSynchronize(x->stream));
+    return xnor_nn_success;
+}
+
+xnor_nn_status_t run_conv(const Plan &p, ResCtx *x, xnor_nn_resources_t res, float *dst,
+                          int32_t *sums) {
+    switch (p.family) {
+        case kPopc:
+            CU(launch_conv_popc(p, (const uint32_t *)res[xnor_nn_resource_bin_src],
+                                (const uint32_t *)res[xnor_nn_resource_bin_weights],
+                                (const float *)res[xnor_nn_resource_alpha],
+                                (const float *)res[xnor_nn_resource_k],
+                                (const int32_t *)res[xnor_nn_resource_operations_count], dst, sums,
+                                x->stream));
+            return xnor_nn_success;
+        default:
+            snprintf(t_last_error, sizeof t_last_error, "kernel family %s is not built in",
+                     family_name(p.family));
+            return xnor_nn_unimplemented;
+    }
+}
+
+// Replaces upstream BcastConvolution::exec (src/default/bcast_convolution_default.cpp:107-211,
+// src/x86/bcast_convolution_avx.cpp:221-352).
+xnor_nn_status_t exec_forward(const xnor_nn_convolution_t *c, xnor_nn_resources_t res) {
+    if (!c || !res || !res[xnor_nn_resource_bin_src] || !res[xnor_nn_resource_bin_weights] ||
+        !res[xnor_nn_resource_user_dst] || !res[xnor_nn_resource_k] ||
+        !res[xnor_nn_resource_alpha] || !res[xnor_nn_resource_operations_count])
+        return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x) return xnor_nn_error_invalid_input;
+    if (!p->formats_ok) return xnor_nn_unimplemented;
+    DeviceGuard dg(x->device);
+    log_exec(*p, "forward");
+    void *user = res[xnor_nn_resource_user_dst];
+    const bool direct = on_device(user);
+    float *dst = (float *)user;
+    if (!direct) {
+        xnor_nn_status_t st = ensure_stage(x, 2, dst_elems(*p) * sizeof(float));
+        if (st != xnor_nn_success) return st;
+        dst = (float *)x->stage[2];
+    }
+    xnor_nn_status_t st = run_conv(*p, x, res, dst, nullptr);
+    if (st != xnor_nn_success) return st;
+    if (!direct) {
+        CU(cudaMemcpyAsync(user, dst, dst_elems(*p) * sizeof(float), cudaMemcpyDeviceToHost,
+                           x->stream));
+        CU(cudaStreamSynchronize(x->stream));
+    }
+    return xnor_nn_success;
+}
+
+xnor_nn_status_t init_common(xnor_nn_convolution_t *c, xnor_nn_algorithm_t algorithm,
+                             xnor_nn_tensor_format_t src_fmt, xnor_nn_tensor_format_t weights_fmt,
+                             xnor_nn_tensor_format_t dst_fmt, int mb, int oc, int ic, int ih,
+                             int iw, int kh, int kw, int sh, int sw, int ph, int pw,
+                             Family family) {
+    // Output extent as upstream computes it: both from pw (src/common_convolution.cpp:16-17).
+    c->algorithm = algorithm;
+    c->mb = mb;
+    c->ic = ic; c->ih = ih; c->iw = iw;
+    c->oc = oc;
+    c->oh = (ih + 2 * pw - kh) / sh + 1;
+    c->ow = (iw + 2 * pw - kw) / sw + 1;
+    c->sh = sh; c->sw = sw;
+    c->kh = kh; c->kw = kw;
+    c->ph = ph; c->pw = pw;
+    c->src_format = src_fmt;
+    c->weights_format = weights_fmt;
+    c->dst_format = dst_fmt;
+    for (int i = 0; i < xnor_nn_resource_number; i++) c->resource_size[i] = 0;
+
+    Plan *p = new (std::nothrow) Plan;
+    c->state = p;
+    c->binarize_weights = exec_binarize_weights;
+    c->binarize_data = exec_binarize_data;
+    c->calculate_k = exec_calculate_k;
+    c->forward = exec_forward;
+    if (!p) return xnor_nn_success;  // executors report the missing plan as bad input
+    make_plan(p, c, family);
+    for (int i = xnor_nn_resource_internal; i < xnor_nn_resource_number; i++)
+        c->resource_size[i] = p->bytes[i];
+    if (verbose())
+        printf("xnor_nn_b200: init: convolution: kernel=%s mb=%d ic=%d ih=%d iw=%d oc=%d oh=%d "
+               "ow=%d kh=%d kw=%d sh=%d sw=%d ph=%d pw=%d\n",
+               family_name(p->family), mb, ic, ih, iw, oc, c->oh, c->ow, kh, kw, sh, sw, ph, pw);
+    return xnor_nn_success;
+}
+
+}  // namespace
+
+// ---- upstream interface ------------------------------------------------------------------------
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+void xnor_nn_get_status_message(char *msg, xnor_nn_status_t status) {
+    const char *text = "unknown";
+    switch (status) {
+        case xnor_nn_success: text = "success"; break;
+        case xnor_nn_error_memory: text = "memory_error"; break;
+        case xnor_nn_error_invalid_input: text = "bad_input"; break;
+        case xnor_nn_unimplemented: text = "unimplemented"; break;
+    }
+    strcpy(msg, text);
+}
+
+xnor_nn_status_t xnor_nn_init_convolution(xnor_nn_convolution_t *c,
+                                          const xnor_nn_algorithm_t algorithm,
+                                          const xnor_nn_tensor_format_t src_fmt,
+                                          const xnor_nn_tensor_format_t weights_fmt,
+                                          const xnor_nn_tensor_format_t dst_fmt, int mb, int oc,
+                                          int ic, int ih, int iw, int kh, int kw, int sh, int sw,
+                                          int ph, int pw) {
+    return init_common(c, algorithm, src_fmt, weights_fmt, dst_fmt, mb, oc, ic, ih, iw, kh, kw,
+                       sh, sw, ph, pw, kAuto);
+}
+
+xnor_nn_status_t xnor_nn_b200_init_convolution(xnor_nn_convolution_t *c,
+                                               const xnor_nn_algorithm_t algorithm,
+                                               const xnor_nn_tensor_format_t src_fmt,
+                                               const xnor_nn_tensor_format_t weights_fmt,
+                                               const xnor_nn_tensor_format_t dst_fmt, int mb,
+                                               int oc, int ic, int ih, int iw, int kh, int kw,
+                                               int sh, int sw, int ph, int pw,
+                                               xnor_nn_b200_kernel_t kernel) {
+    return init_common(c, algorithm, src_fmt, weights_fmt, dst_fmt, mb, oc, ic, ih, iw, kh, kw,
+                       sh, sw, ph, pw, (Family)(int)kernel);
+}
+
+xnor_nn_b200_kernel_t xnor_nn_b200_kernel_of(const xnor_nn_convolution_t *c) {
+    const Plan *p = plan_of(c);
+    return p ? (xnor_nn_b200_kernel_t)(int)p->family : xnor_nn_b200_kernel_auto;
+}
+
+void xnor_nn_destroy_convolution(xnor_nn_convolution_t *c) {
+    if (!c) return;
+    delete static_cast<Plan *>(c->state);
+    c->state = nullptr;
+}
+
+void xnor_nn_free_resources(xnor_nn_resources_t res) {
+    if (!res) return;
+    ResCtx *x = nullptr;
+    if (res[xnor_nn_resource_alpha]) {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_ctx.find(res[xnor_nn_resource_alpha]);
+        if (it != g_ctx.end()) {
+            x = it->second;
+            g_ctx.erase(it);
+        }
+    }
+    if (x) {
+        DeviceGuard dg(x->device);
+        cudaStreamSynchronize(x->stream);
+        for (int i = xnor_nn_resource_internal; i < xnor_nn_resource_number; i++)
+            if (res[i]) cudaFree(res[i]);
+        for (int i = 0; i < 3; i++)
+            if (x->stage[i]) cudaFree(x->stage[i]);
+        if (x->sums_stage) cudaFree(x->sums_stage);
+        if (x->own_stream) cudaStreamDestroy(x->own_stream);
+        (void)cudaGetLastError();
+        delete x;
+    }
+    // Slots this library did not create (no context on record) are only cleared.
+    for (int i = xnor_nn_resource_internal; i < xnor_nn_resource_number; i++) res[i] = nullptr;
+}
+
+xnor_nn_status_t xnor_nn_allocate_resources(const xnor_nn_convolution_t *c,
+                                            xnor_nn_resources_t res) {
+    if (!c || !res) return xnor_nn_error_invalid_input;
+    for (int i = xnor_nn_resource_internal; i < xnor_nn_resource_number; i++) res[i] = nullptr;
+    ResCtx *x = new (std::nothrow) ResCtx;
+    if (!x) return xnor_nn_error_memory;
+    cudaError_t e = cudaGetDevice(&x->device);
+    if (e == cudaSuccess) e = cudaStreamCreate(&x->own_stream);
+    x->stream = x->own_stream;
+    for (int i = xnor_nn_resource_internal; e == cudaSuccess && i < xnor_nn_resource_number; i++) {
+        const size_t bytes = c->resource_size[i] ? c->resource_size[i] : 16;
+        e = cudaMalloc(&res[i], bytes);
+        // Zero once: the framed layouts rely on their border rows and channel tails being 0.
+        if (e == cudaSuccess) e = cudaMemsetAsync(res[i], 0, bytes, x->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(x->stream);
+    if (e != cudaSuccess) {
+        for (int i = xnor_nn_resource_internal; i < xnor_nn_resource_number; i++) {
+            if (res[i]) cudaFree(res[i]);
+            res[i] = nullptr;
+        }
+        if (x->own_stream) cudaStreamDestroy(x->own_stream);
+        delete x;
+        fail(e, "xnor_nn_allocate_resources");
+        return xnor_nn_error_memory;
+    }
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_ctx[res[xnor_nn_resource_alpha]] = x;
+    return xnor_nn_success;
+}
+
+// Host helper of the training backward pass, upstream src/binarize_weights_float.cpp:3-25:
+// to = sign(from) * mean(from). Upstream sums with an unsynchronised OpenMP reduction; this
+// sums in index order, which is what upstream computes when run on one thread.
+void xnor_nn_binarize_weights_float(const xnor_nn_convolution_t *c, const float *from,
+                                    float *to) {
+    if (!c || !from || !to) return;
+    const int elems = c->oc * c->ic * c->kh * c->kw;
+    const float scale = 1.f / elems;
+    float mean = 0.f;
+    for (int i = 0; i < elems; i++) mean += from[i];
+    mean *= scale;
+    for (int i = 0; i < elems; i++) to[i] = (from[i] >= .0f ? 1.f : -1.f) * mean;
+}
+
+// ---- extensions --------------------------------------------------------------------------------
+
+xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_resources_t res) {
+    if (!c || !res || !res[xnor_nn_resource_user_src] || !res[xnor_nn_resource_user_dst] ||
+        !res[xnor_nn_resource_bin_src] || !res[xnor_nn_resource_bin_weights] ||
+        !res[xnor_nn_resource_a] || !res[xnor_nn_resource_k] || !res[xnor_nn_resource_alpha] ||
+        !res[xnor_nn_resource_operations_count])
+        return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x) return xnor_nn_error_invalid_input;
+    if (!p->formats_ok) return xnor_nn_unimplemented;
+    DeviceGuard dg(x->device);
+    log_exec(*p, "fused forward");
+    const void *src = nullptr;
+    bool staged = false;
+    xnor_nn_status_t st = stage_in(x, 0, res[xnor_nn_resource_user_src], src_bytes(*p), &src, &staged);
+    if (st != xnor_nn_success) return st;
+    void *user = res[xnor_nn_resource_user_dst];
+    const bool direct = on_device(user);
+    float *dst = (float *)user;
+    if (!direct) {
+        st = ensure_stage(x, 2, dst_elems(*p) * sizeof(float));
+        if (st != xnor_nn_success) return st;
+        dst = (float *)x->stage[2];
+    }
+    CU(launch_binarize_data(*p, (const float *)src, res[xnor_nn_resource_bin_src],
+                            (float *)res[xnor_nn_resource_a], x->stream));
+    CU(launch_box_filter(*p, (const float *)res[xnor_nn_resource_a],
+                         (float *)res[xnor_nn_resource_k], x->stream));
+    st = run_conv(*p, x, res, dst, nullptr);
+    if (st != xnor_nn_success) return st;
+    if (!direct)
+        CU(cudaMemcpyAsync(user, dst, dst_elems(*p) * sizeof(float), cudaMemcpyDeviceToHost,
+                           x->stream));
+    if (!direct || staged) CU(cudaStreamSynchronize(x->stream));
+    return xnor_nn_success;
+}
+
+xnor_nn_status_t xnor_nn_b200_forward_sums(const xnor_nn_convolution_t *c,
+                                           xnor_nn_resources_t res, int32_t *sums) {
+    if (!c || !res || !sums || !res[xnor_nn_resource_bin_src] ||
+        !res[xnor_nn_resource_bin_weights] || !res[xnor_nn_resource_operations_count] ||
+        !res[xnor_nn_resource_alpha] || !res[xnor_nn_resource_k])
+        return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x) return xnor_nn_error_invalid_input;
+    DeviceGuard dg(x->device);
+    const size_t bytes = dst_elems(*p) * sizeof(int32_t);
+    const bool direct = on_device(sums);
+    int32_t *dev = sums;
+    if (!direct) {
+        if (x->sums_bytes < bytes) {
+            if (x->sums_stage) CU(cudaFree(x->sums_stage));
+            x->sums_stage = nullptr;
+            x->sums_bytes = 0;
+            CU(cudaMalloc(&x->sums_stage, bytes));
+            x->sums_bytes = bytes;
+        }
+        dev = x->sums_stage;
+    }
+    xnor_nn_status_t st = run_conv(*p, x, res, nullptr, dev);
+    if (st != xnor_nn_success) return st;
+    if (!direct) {
+        CU(cudaMemcpyAsync(sums, dev, bytes, cudaMemcpyDeviceToHost, x->stream));
+        CU(cudaStreamSynchronize(x->stream));
+    }
+    return xnor_nn_success;
+}
+
+xnor_nn_status_t xnor_nn_b200_read_resource(const xnor_nn_convolution_t *c,
+                                            xnor_nn_resources_t res, int slot, void *host_dst,
+                                            size_t bytes) {
+    if (!c || !res || !host_dst || slot < xnor_nn_resource_internal ||
+        slot >= xnor_nn_resource_number || !res[slot] || bytes > c->resource_size[slot])
+        return xnor_nn_error_invalid_input;
+    ResCtx *x = find_ctx(res);
+    if (!x) return xnor_nn_error_invalid_input;
+    DeviceGuard dg(x->device);
+    CU(cudaMemcpyAsync(host_dst, res[slot], bytes, cudaMemcpyDeviceToHost, x->stream));
+    CU(cudaStreamSynchronize(x->stream));
+    return xnor_nn_success;
+}
+
+xnor_nn_status_t xnor_nn_b200_set_stream(xnor_nn_resources_t res, void *cuda_stream) {
+    ResCtx *x = find_ctx(res);
+    if (!x) return xnor_nn_error_invalid_input;
+    DeviceGuard dg(x->device);
+    CU(cudaStreamSynchronize(x->stream));
+    x->stream = cuda_stream ? (cudaStream_t)cuda_stream : x->own_stream;
+    return xnor_nn_success;
+}
+
+void *xnor_nn_b200_get_stream(xnor_nn_resources_t res) {
+    ResCtx *x = find_ctx(res);
+    return x ? (void *)x->stream : nullptr;
+}
+
+xnor_nn_status_t xnor_nn_b200_synchronize(xnor_nn_resources_t res) {
+    ResCtx *x = find_ctx(res);
+    if (!x) return xnor_nn_error_invalid_input;
+    DeviceGuard dg(x->device);
+    CU(cudaStreamSynchronize(x->stream));
+    return xnor_nn_success;
+}
+
+const char *xnor_nn_b200_last_error(void) { return t_last_error; }
+
+long xnor_nn_b200_kernel_launches(void) { return g_kernel_launches.load(); }
+
+}  // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,195 @@
+// Activation-side kernels: sign packing with the fused mean-|x| map, and the K box filter.
+//
+// All three are bound by HBM bandwidth: the fp32 source (4 B per element) is read exactly once
+// and 1/32 (bits) or 1/4 (int8) of that is written. One thread owns one pixel and walks its
+// channels in ascending order, so the mean-|x| sum is accumulated in the very order upstream
+// uses (src/bcast_calculate_k.cpp:55-65) and rounds identically; with an NCHW source the 32
+// lanes of a warp read 32 neighbouring pixels of one channel plane, a full 128-byte line.
+#include "kernels.cuh"
+
+namespace xb200 {
+
+namespace {
+
+enum OutKind { kBitsDense = 0, kBitsFramed = 1, kBytesFramed = 2 };
+
+struct BinArgs {
+    const float *src;
+    void *out;
+    float *a;
+    long n_px;        // mb*ih*iw
+    int ic, hw, iw;   // hw = ih*iw
+    long img_stride;  // elements between images in src
+    long c_stride;    // elements between channels of one pixel
+    long px_stride;   // elements between pixels of one image
+    float inv_ic;
+    int words;        // 32-bit words per packed row (icw, or icp/4 for bytes)
+    int wp, hp, lead, ih;
+};
+
+__device__ __forceinline__ unsigned sign_clear(float x) { return (~__float_as_uint(x)) >> 31; }
+
+// Row of the packed matrix that pixel (n, h, w) owns.
+template <int KIND>
+__device__ __forceinline__ long packed_row(const BinArgs &g, long px) {
+    if (KIND == kBitsDense) return px;
+    const int n = (int)(px / g.hw);
+    const int r = (int)(px - (long)n * g.hw);
+    const int h = r / g.iw, w = r - h * g.iw;
+    return g.lead + ((long)n * g.hp + h) * g.wp + w;
+}
+
+template <int KIND, bool WITH_A, bool WITH_PACK>
+__global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
+    const long px = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (px >= g.n_px) return;
+    const int n = (int)(px / g.hw);
+    const int r = (int)(px - (long)n * g.hw);
+    const float *p = g.src + n * g.img_stride + r * g.px_stride;
+    uint32_t *row = WITH_PACK ? (uint32_t *)g.out + packed_row<KIND>(g, px) * g.words : nullptr;
+
+    float acc = 0.f;
+    const int full = g.ic & ~31;
+    int c = 0;
+    for (; c < full; c += 32) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = __ldg(p + (long)(c + i) * g.c_stride);
+        if (WITH_A) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) acc = __fadd_rn(acc, __fmul_rn(fabsf(v[i]), g.inv_ic));
+        }
+        if (WITH_PACK) {
+            if (KIND == kBytesFramed) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    uint32_t w = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        w |= (sign_clear(v[4 * j + i]) ? 0x01u : 0xFFu) << (8 * i);
+                    row[c / 4 + j] = w;
+                }
+            } else {
+                uint32_t w = 0;
+#pragma unroll
+                for (int i = 0; i < 32; i++) w = (w << 1) | sign_clear(v[i]);
+                row[c / 32] = w;
+            }
+        }
+    }
+    if (c < g.ic) {  // channel tail: absent channels pack as zero
+        uint32_t wbits = 0;
+        uint32_t wbytes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int i = 0; i < 32; i++) {
+            unsigned bit = 0;
+            if (c + i < g.ic) {
+                const float x = __ldg(p + (long)(c + i) * g.c_stride);
+                if (WITH_A) acc = __fadd_rn(acc, __fmul_rn(fabsf(x), g.inv_ic));
+                bit = sign_clear(x);
+                wbytes[i / 4] |= (bit ? 0x01u : 0xFFu) << (8 * (i % 4));
+            }
+            wbits = (wbits << 1) | bit;
+        }
+        if (WITH_PACK) {
+            if (KIND == kBytesFramed) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) row[c / 4 + j] = wbytes[j];
+            } else {
+                row[c / 32] = wbits;
+            }
+        }
+        c += 32;
+    }
+    if (WITH_PACK && KIND == kBytesFramed) {
+        // chunk padding beyond the last 32-channel group stays zero
+        for (int j = c / 4; j < g.words; j++) row[j] = 0u;
+    }
+    if (WITH_A) g.a[px] = acc;
+}
+
+struct BoxArgs {
+    const float *a;
+    float *k;
+    long n_out;
+    int ih, iw, oh, ow, kh, kw, sh, sw, ph, pw;
+    float inv_khw;
+};
+
+__global__ void __launch_bounds__(256) box_filter_kernel(const BoxArgs g) {
+    const long o = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= g.n_out) return;
+    const int ohw = g.oh * g.ow;
+    const int n = (int)(o / ohw);
+    const int r = (int)(o - (long)n * ohw);
+    const int oh = r / g.ow, ow = r - oh * g.ow;
+    const float *img = g.a + (long)n * g.ih * g.iw;
+    float acc = 0.f;
+    for (int kh = 0; kh < g.kh; kh++) {
+        const int ih = oh * g.sh - g.ph + kh;
+        if (ih < 0 || ih >= g.ih) continue;
+        for (int kw = 0; kw < g.kw; kw++) {
+            const int iw = ow * g.sw - g.pw + kw;
+            if (iw < 0 || iw >= g.iw) continue;
+            acc = __fadd_rn(acc, __fmul_rn(__ldg(img + ih * g.iw + iw), g.inv_khw));
+        }
+    }
+    g.k[o] = acc;
+}
+
+BinArgs bin_args(const Plan &p, const float *src, void *out, float *a) {
+    BinArgs g;
+    g.src = src; g.out = out; g.a = a;
+    g.n_px = (long)p.mb * p.ih * p.iw;
+    g.ic = p.ic; g.hw = p.ih * p.iw; g.iw = p.iw; g.ih = p.ih;
+    g.img_stride = (long)p.ic * p.ih * p.iw;
+    g.c_stride = p.src_nhwc ? 1 : (long)p.ih * p.iw;
+    g.px_stride = p.src_nhwc ? p.ic : 1;
+    g.inv_ic = p.inv_ic;
+    g.words = p.family == kTcgen05 ? p.icp / 4 : p.icw;
+    g.wp = p.wp; g.hp = p.hp; g.lead = p.lead;
+    return g;
+}
+
+template <bool WITH_A, bool WITH_PACK>
+cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
+    const int threads = 128;
+    const unsigned blocks = (unsigned)((g.n_px + threads - 1) / threads);
+    if (blocks == 0) return cudaSuccess;
+    switch (p.family) {
+        case kPopc: binarize_kernel<kBitsDense, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
+        case kMmaB1: binarize_kernel<kBitsFramed, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
+        default: binarize_kernel<kBytesFramed, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
+    }
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_binarize_data(const Plan &p, const float *src, void *bin_src, float *a,
+                                 cudaStream_t s) {
+    const BinArgs g = bin_args(p, src, bin_src, a);
+    return a ? launch_bin<true, true>(p, g, s) : launch_bin<false, true>(p, g, s);
+}
+
+cudaError_t launch_mean_abs(const Plan &p, const float *src, float *a, cudaStream_t s) {
+    const BinArgs g = bin_args(p, src, nullptr, a);
+    return launch_bin<true, false>(p, g, s);
+}
+
+cudaError_t launch_box_filter(const Plan &p, const float *a, float *k, cudaStream_t s) {
+    BoxArgs g;
+    g.a = a; g.k = k;
+    g.n_out = (long)p.mb * p.oh * p.ow;
+    g.ih = p.ih; g.iw = p.iw; g.oh = p.oh; g.ow = p.ow; g.kh = p.kh; g.kw = p.kw;
+    g.sh = p.sh; g.sw = p.sw; g.ph = p.ph; g.pw = p.pw;
+    g.inv_khw = p.inv_khw;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((g.n_out + threads - 1) / threads);
+    if (blocks == 0) return cudaSuccess;
+    box_filter_kernel<<<blocks, threads, 0, s>>>(g);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace xb200

@@ -1,0 +1,106 @@
+#include "plan.hpp"
+
+#include <cstdlib>
+#include <cstring>
+
+namespace xb200 {
+
+int div_up_i(int a, int b) { return (a + b - 1) / b; }
+
+const char *family_name(Family f) {
+    switch (f) {
+        case kPopc: return "popc";
+        case kMmaB1: return "mma_b1";
+        case kTcgen05: return "tcgen05_i8";
+        default: return "auto";
+    }
+}
+
+static Family family_from_env() {
+    const char *e = getenv("XNOR_NN_B200_KERNEL");
+    if (!e) return kAuto;
+    if (!strcmp(e, "popc")) return kPopc;
+    if (!strcmp(e, "mma_b1")) return kMmaB1;
+    if (!strcmp(e, "tcgen05_i8") || !strcmp(e, "tcgen05")) return kTcgen05;
+    return kAuto;
+}
+
+// The two tensor-core families walk a zero-framed image with constant row shifts per filter
+// tap, which only describes a unit-stride convolution whose output extent matches the padding
+// actually applied (upstream derives the output height from pw, src/common_convolution.cpp:16).
+static bool frame_walk_ok(const Plan &p) {
+    return p.sh == 1 && p.sw == 1 && p.oh == p.ih + 2 * p.ph - p.kh + 1 &&
+           p.ow == p.iw + 2 * p.pw - p.kw + 1 && p.oh > 0 && p.ow > 0 &&
+           p.kh - 1 - p.ph <= p.ph + p.ih && p.kw - 1 - p.pw <= p.iw;
+}
+
+void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
+    memset(p, 0, sizeof(*p));
+    p->mb = c->mb; p->ic = c->ic; p->ih = c->ih; p->iw = c->iw;
+    p->oc = c->oc; p->oh = c->oh; p->ow = c->ow;
+    p->kh = c->kh; p->kw = c->kw; p->sh = c->sh; p->sw = c->sw; p->ph = c->ph; p->pw = c->pw;
+    p->src_nhwc = c->src_format == xnor_nn_data_format_nhwc;
+    p->w_hwio = c->weights_format == xnor_nn_weights_format_hwio;
+    p->dst_nhwc = c->dst_format == xnor_nn_data_format_nhwc;
+    p->formats_ok =
+        (c->src_format == xnor_nn_data_format_nchw || c->src_format == xnor_nn_data_format_nhwc) &&
+        (c->weights_format == xnor_nn_weights_format_oihw ||
+         c->weights_format == xnor_nn_weights_format_hwio) &&
+        (c->dst_format == xnor_nn_data_format_nchw || c->dst_format == xnor_nn_data_format_nhwc);
+
+    p->inv_ic = 1.f / p->ic;
+    p->inv_khw = 1.f / p->kh / p->kw;
+    p->inv_chw = 1.f / (p->ic * p->kh * p->kw);
+
+    Family f = requested == kAuto ? family_from_env() : requested;
+    const bool walk = frame_walk_ok(*p);
+    if (f == kAuto) f = walk ? kTcgen05 : kPopc;
+    if ((f == kMmaB1 || f == kTcgen05) && !walk) f = kPopc;
+    p->family = f;
+
+    const size_t px_in = (size_t)p->mb * p->ih * p->iw;
+    const size_t px_out = (size_t)p->mb * p->oh * p->ow;
+    p->bytes[xnor_nn_resource_alpha] = (size_t)p->oc * sizeof(float);
+    p->bytes[xnor_nn_resource_a] = px_in * sizeof(float);
+    p->bytes[xnor_nn_resource_k] = px_out * sizeof(float);
+    p->bytes[xnor_nn_resource_operations_count] = (size_t)p->oh * p->ow * sizeof(int32_t);
+
+    p->icw = div_up_i(p->ic, 32);
+    p->wp = p->iw + p->pw;
+    p->hp = p->ih + p->ph;
+    p->q_total = (long)p->mb * p->hp * p->wp;
+
+    if (f == kPopc) {
+        p->ocp = div_up_i(p->oc, 8) * 8;
+        p->bytes[xnor_nn_resource_bin_src] = px_in * p->icw * sizeof(uint32_t);
+        p->bytes[xnor_nn_resource_bin_weights] =
+            (size_t)p->kh * p->kw * p->icw * p->ocp * sizeof(uint32_t);
+    } else if (f == kMmaB1) {
+        // K runs over (tap, 32-bit word); one mma consumes 8 words, so the words of a pixel
+        // are padded to a multiple of 8 only if that wastes little, else taps are fused: the
+        // kernel handles both through icw8 = words per pixel it walks.
+        p->icw = div_up_i(p->ic, 32);
+        p->ocp = div_up_i(p->oc, 8) * 8;
+        p->lead = p->ph * p->wp + p->pw;
+        p->rows = p->lead + p->q_total + 256 + (long)p->kh * p->wp + p->kw;
+        p->bytes[xnor_nn_resource_bin_src] = (size_t)p->rows * p->icw * sizeof(uint32_t);
+        p->bytes[xnor_nn_resource_bin_weights] =
+            (size_t)p->kh * p->kw * p->icw * p->ocp * sizeof(uint32_t);
+    } else {
+        p->kchunk = p->ic > 64 && (div_up_i(p->ic, 32) * 32) % 128 == 0 ? 128
+                    : (div_up_i(p->ic, 32) * 32) % 64 == 0             ? 64
+                                                                        : 32;
+        p->icp = div_up_i(p->ic, p->kchunk) * p->kchunk;
+        p->ocp16 = div_up_i(p->oc, 16) * 16;
+        // Largest multiple of 16 not above 256 that splits ocp16 evenly.
+        int tiles = div_up_i(p->ocp16, 256);
+        while ((p->ocp16 / 16) % tiles) tiles++;
+        p->n_tile = p->ocp16 / tiles;
+        p->lead = p->ph * p->wp + p->pw;
+        p->rows = p->lead + p->q_total + 256 + (long)p->kh * p->wp + p->kw;
+        p->bytes[xnor_nn_resource_bin_src] = (size_t)p->rows * p->icp;
+        p->bytes[xnor_nn_resource_bin_weights] = (size_t)p->kh * p->kw * p->ocp16 * p->icp;
+    }
+}
+
+}  // namespace xb200

@@ -1,0 +1,121 @@
+// Weight-side kernels: sign packing, alpha = mean |w| per output channel, and the per-pixel
+// count of contributing operands. They run once per weight change (a few hundred KB of
+// output), off the per-minibatch path, so they favour exactness over speed: alpha is summed by
+// one thread per output channel in upstream's (ic, kh, kw) order
+// (src/bcast_binarize_weights.cpp:99-114) and therefore rounds identically.
+#include "kernels.cuh"
+
+namespace xb200 {
+
+namespace {
+
+struct WArgs {
+    const float *w;
+    int oc, ic, kh, kw;
+    bool hwio;
+};
+
+__device__ __forceinline__ long w_index(const WArgs &g, int oc, int c, int kh, int kw) {
+    return g.hwio ? (((long)kh * g.kw + kw) * g.ic + c) * g.oc + oc
+                  : (((long)oc * g.ic + c) * g.kh + kh) * g.kw + kw;
+}
+
+__device__ __forceinline__ unsigned sign_clear(float x) { return (~__float_as_uint(x)) >> 31; }
+
+// bits: uint32 [tap][word][ocp]
+__global__ void pack_weight_bits_kernel(const WArgs g, uint32_t *out, int icw, int ocp) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long total = (long)g.kh * g.kw * icw * ocp;
+    if (i >= total) return;
+    const int oc = (int)(i % ocp);
+    const int word = (int)((i / ocp) % icw);
+    const int tap = (int)(i / ((long)ocp * icw));
+    const int kh = tap / g.kw, kw = tap - kh * g.kw;
+    uint32_t v = 0;
+    for (int b = 0; b < 32; b++) {
+        const int c = word * 32 + b;
+        unsigned bit = 0;
+        if (oc < g.oc && c < g.ic) bit = sign_clear(__ldg(g.w + w_index(g, oc, c, kh, kw)));
+        v = (v << 1) | bit;
+    }
+    out[i] = v;
+}
+
+// bytes: int8 [tap][ocp16][icp], +1 / -1, zero where the channel or the filter does not exist
+__global__ void pack_weight_bytes_kernel(const WArgs g, uint32_t *out, int icp, int ocp16) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int groups = icp / 4;
+    const long total = (long)g.kh * g.kw * ocp16 * groups;
+    if (i >= total) return;
+    const int grp = (int)(i % groups);
+    const int oc = (int)((i / groups) % ocp16);
+    const int tap = (int)(i / ((long)groups * ocp16));
+    const int kh = tap / g.kw, kw = tap - kh * g.kw;
+    uint32_t v = 0;
+    for (int b = 0; b < 4; b++) {
+        const int c = grp * 4 + b;
+        if (oc < g.oc && c < g.ic)
+            v |= (sign_clear(__ldg(g.w + w_index(g, oc, c, kh, kw))) ? 0x01u : 0xFFu) << (8 * b);
+    }
+    out[i] = v;
+}
+
+__global__ void alpha_kernel(const WArgs g, float *alpha, float inv_chw) {
+    const int oc = blockIdx.x * blockDim.x + threadIdx.x;
+    if (oc >= g.oc) return;
+    float acc = 0.f;
+    for (int c = 0; c < g.ic; c++)
+        for (int kh = 0; kh < g.kh; kh++)
+            for (int kw = 0; kw < g.kw; kw++)
+                acc = __fadd_rn(acc, __fmul_rn(fabsf(__ldg(g.w + w_index(g, oc, c, kh, kw))),
+                                               inv_chw));
+    alpha[oc] = acc;
+}
+
+__global__ void op_count_kernel(int32_t *op_c, int ic, int ih, int iw, int oh, int ow, int kh,
+                                int kw, int sh, int sw, int ph, int pw) {
+    const int o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= oh * ow) return;
+    const int y = o / ow, x = o - y * ow;
+    int taps = 0;
+    for (int i = 0; i < kh; i++) {
+        const int h = y * sh - ph + i;
+        if (h < 0 || h >= ih) continue;
+        for (int j = 0; j < kw; j++) {
+            const int w = x * sw - pw + j;
+            taps += (w >= 0 && w < iw);
+        }
+    }
+    op_c[o] = taps * ic;
+}
+
+}  // namespace
+
+cudaError_t launch_binarize_weights(const Plan &p, const float *w, void *bin_w, float *alpha,
+                                    int32_t *op_c, cudaStream_t s) {
+    WArgs g;
+    g.w = w; g.oc = p.oc; g.ic = p.ic; g.kh = p.kh; g.kw = p.kw; g.hwio = p.w_hwio;
+    const int threads = 128;
+    if (p.family == kTcgen05) {
+        const long total = (long)p.kh * p.kw * p.ocp16 * (p.icp / 4);
+        pack_weight_bytes_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, s>>>(
+            g, (uint32_t *)bin_w, p.icp, p.ocp16);
+    } else {
+        const long total = (long)p.kh * p.kw * p.icw * p.ocp;
+        pack_weight_bits_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, s>>>(
+            g, (uint32_t *)bin_w, p.icw, p.ocp);
+    }
+    note_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    alpha_kernel<<<(p.oc + 31) / 32, 32, 0, s>>>(g, alpha, p.inv_chw);
+    note_launch();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    op_count_kernel<<<(p.oh * p.ow + threads - 1) / threads, threads, 0, s>>>(
+        op_c, p.ic, p.ih, p.iw, p.oh, p.ow, p.kh, p.kw, p.sh, p.sw, p.ph, p.pw);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace xb200
