@@ -34,6 +34,9 @@ static bool frame_walk_ok(const Plan &p) {
            p.kh - 1 - p.ph <= p.ph + p.ih && p.kw - 1 - p.pw <= p.iw;
 }
 
+// Families whose convolution kernel is compiled into this library.
+static bool family_built(Family f) { return f == kPopc; }
+
 void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
     memset(p, 0, sizeof(*p));
     p->mb = c->mb; p->ic = c->ic; p->ih = c->ih; p->iw = c->iw;
@@ -56,6 +59,7 @@ void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
     const bool walk = frame_walk_ok(*p);
     if (f == kAuto) f = walk ? kTcgen05 : kPopc;
     if ((f == kMmaB1 || f == kTcgen05) && !walk) f = kPopc;
+    if (!family_built(f)) f = kPopc;
     p->family = f;
 
     const size_t px_in = (size_t)p->mb * p->ih * p->iw;
