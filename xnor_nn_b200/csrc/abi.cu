@@ -62,6 +62,7 @@ struct ResCtx {
     size_t stage_bytes[3] = {0, 0, 0};
     int32_t *sums_stage = nullptr;
     size_t sums_bytes = 0;
+    int *error_word = nullptr;  // device int: set by a kernel whose bounded wait ran out
 };
 
 std::mutex g_mu;
@@ -117,6 +118,20 @@ xnor_nn_status_t stage_in(ResCtx *x, int which, const void *user, size_t bytes,
     CU(cudaMemcpyAsync(x->stage[which], user, bytes, cudaMemcpyHostToDevice, x->stream));
     *dev = x->stage[which];
     *staged = true;
+    return xnor_nn_success;
+}
+
+// Waits for the context's stream and turns a kernel-side give-up into a status code.
+xnor_nn_status_t sync_and_check(ResCtx *x) {
+    CU(cudaStreamSynchronize(x->stream));
+    int word = 0;
+    CU(cudaMemcpy(&word, x->error_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (word != 0) {
+        snprintf(t_last_error, sizeof t_last_error,
+                 "a kernel gave up waiting (site %d); results of this call are invalid", word);
+        CU(cudaMemset(x->error_word, 0, sizeof(int)));
+        return xnor_nn_unimplemented;
+    }
     return xnor_nn_success;
 }
 
@@ -214,6 +229,13 @@ xnor_nn_status_t run_conv(const Plan &p, ResCtx *x, xnor_nn_resources_t res, flo
                                 (const int32_t *)res[xnor_nn_resource_operations_count], dst, sums,
                                 x->stream));
             return xnor_nn_success;
+        case kTcgen05:
+            CU(launch_conv_tcgen05(p, res[xnor_nn_resource_bin_src],
+                                   res[xnor_nn_resource_bin_weights],
+                                   (const float *)res[xnor_nn_resource_alpha],
+                                   (const float *)res[xnor_nn_resource_k], dst, sums,
+                                   x->error_word, x->stream));
+            return xnor_nn_success;
         default:
             snprintf(t_last_error, sizeof t_last_error, "kernel family %s is not built in",
                      family_name(p.family));
@@ -247,7 +269,7 @@ xnor_nn_status_t exec_forward(const xnor_nn_convolution_t *c, xnor_nn_resources_
     if (!direct) {
         CU(cudaMemcpyAsync(user, dst, dst_elems(*p) * sizeof(float), cudaMemcpyDeviceToHost,
                            x->stream));
-        CU(cudaStreamSynchronize(x->stream));
+        return sync_and_check(x);
     }
     return xnor_nn_success;
 }
@@ -360,6 +382,7 @@ void xnor_nn_free_resources(xnor_nn_resources_t res) {
         for (int i = 0; i < 3; i++)
             if (x->stage[i]) cudaFree(x->stage[i]);
         if (x->sums_stage) cudaFree(x->sums_stage);
+        if (x->error_word) cudaFree(x->error_word);
         if (x->own_stream) cudaStreamDestroy(x->own_stream);
         (void)cudaGetLastError();
         delete x;
@@ -383,8 +406,11 @@ xnor_nn_status_t xnor_nn_allocate_resources(const xnor_nn_convolution_t *c,
         // Zero once: the framed layouts rely on their border rows and channel tails being 0.
         if (e == cudaSuccess) e = cudaMemsetAsync(res[i], 0, bytes, x->stream);
     }
+    if (e == cudaSuccess) e = cudaMalloc(&x->error_word, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemsetAsync(x->error_word, 0, sizeof(int), x->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(x->stream);
     if (e != cudaSuccess) {
+        if (x->error_word) cudaFree(x->error_word);
         for (int i = xnor_nn_resource_internal; i < xnor_nn_resource_number; i++) {
             if (res[i]) cudaFree(res[i]);
             res[i] = nullptr;
@@ -448,7 +474,7 @@ xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_re
     if (!direct)
         CU(cudaMemcpyAsync(user, dst, dst_elems(*p) * sizeof(float), cudaMemcpyDeviceToHost,
                            x->stream));
-    if (!direct || staged) CU(cudaStreamSynchronize(x->stream));
+    if (!direct || staged) return sync_and_check(x);
     return xnor_nn_success;
 }
 
@@ -479,7 +505,7 @@ xnor_nn_status_t xnor_nn_b200_forward_sums(const xnor_nn_convolution_t *c,
     if (st != xnor_nn_success) return st;
     if (!direct) {
         CU(cudaMemcpyAsync(sums, dev, bytes, cudaMemcpyDeviceToHost, x->stream));
-        CU(cudaStreamSynchronize(x->stream));
+        return sync_and_check(x);
     }
     return xnor_nn_success;
 }
@@ -516,8 +542,7 @@ xnor_nn_status_t xnor_nn_b200_synchronize(xnor_nn_resources_t res) {
     ResCtx *x = find_ctx(res);
     if (!x) return xnor_nn_error_invalid_input;
     DeviceGuard dg(x->device);
-    CU(cudaStreamSynchronize(x->stream));
-    return xnor_nn_success;
+    return sync_and_check(x);
 }
 
 const char *xnor_nn_b200_last_error(void) { return t_last_error; }

@@ -1,0 +1,450 @@
+// Binary convolution as an implicit GEMM on the 5th-generation tensor cores.
+//
+// Operands are +-1 bytes (0 where a channel, a filter or an image border does not exist), so the
+// int32 accumulator is the signed agreement count S of upstream's kernel
+// (src/default/bcast_convolution_default.cpp:60-103) exactly: products of absent operands are 0,
+// which is upstream's "skip the tap" (:71-72) and its op_c correction (:102) in one.
+//
+//   D[position][filter] += A[position + shift(tap)][channel] * B[tap][filter][channel]
+//
+// The activations live on a zero frame (plan.hpp) on which every filter tap is a constant row
+// shift, so the A tile of a tap is a plain 2-D TMA box at a shifted row; no im2col buffer exists.
+// Positions on the frame border are computed and dropped by the epilogue.
+//
+// One CTA per SM, persistent over (position tile, filter tile) pairs, 192 threads:
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, no multicast) into a ring of
+//               shared-memory stages; completion is counted on an mbarrier per stage
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma.kind::i8 (M=128, N<=256,
+//               K=32 per instruction) from the stages into one of two accumulators in tensor
+//               memory, and tcgen05.commit hands stages back / accumulators on
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (a warp owns 32 TMEM lanes = 32 positions),
+//               scale by alpha[filter] * K[position] in upstream's order and store; runs under
+//               the next tile's MMAs thanks to the second accumulator
+//
+// Every wait on an mbarrier is bounded in time: when the bound is hit the kernel records where
+// in *error, every role winds down, copies in flight are waited for (again bounded), tensor
+// memory is released and the kernel returns.
+#include <cuda.h>
+
+#include "kernels.cuh"
+
+namespace xb200 {
+
+namespace {
+
+constexpr int BM = 128;            // positions per tile = UMMA M = TMEM lanes
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+struct TcArgs {
+    const float *alpha;
+    const float *kmap;
+    float *dst;
+    int32_t *sums;
+    int *error;
+    long q_total;
+    int m_tiles, n_tiles, n_tile;
+    int kchunk, chunks_per_tap, taps, kw, ph, pw;
+    int wp, hp, lead, oh, ow, oc, ocp16;
+    uint32_t idesc;
+    uint32_t desc_hi;  // upper 32 bits of the shared-memory matrix descriptors
+    uint32_t a_bytes, stage_bytes, tx_bytes;
+    int dst_nhwc;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for a barrier phase, giving up after kWaitLimitNs or as soon as another role has given
+// up. Returns false in that case, after recording `code` (first failure wins).
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                       int *error, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            atomicCAS(error, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives on the barrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t *v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+
+__device__ __forceinline__ void tc_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- the kernel --------------------------------------------------------------------------------
+
+struct __align__(8) Control {
+    unsigned long long full[kStages];
+    unsigned long long empty[kStages];
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
+    unsigned long long drain;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    // stages need the swizzle atom's alignment (1024 B); the control block sits in front
+    uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Control *ctl = (Control *)base;
+    uint8_t *stages = base + 1024;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int *abort_flag = &ctl->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(smem_u32(&ctl->full[s]), 1);
+            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&ctl->acc_full[b]), 1);
+            mbar_init(smem_u32(&ctl->acc_empty[b]), 128);
+        }
+        mbar_init(smem_u32(&ctl->drain), 1);
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    const int total_tiles = g.m_tiles * g.n_tiles;
+    const int ksteps = g.taps * g.chunks_per_tap;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t armed = 0;  // bit s: stage s holds a load nobody is known to have consumed
+            uint32_t armed_parity = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
+                const long row0 = (long)g.lead + (long)mt * BM;
+                for (int ks = 0; ks < ksteps; ks++) {
+                    const int tap = ks / g.chunks_per_tap;
+                    const int chunk = ks - tap * g.chunks_per_tap;
+                    const int kh = tap / g.kw, kw = tap - kh * g.kw;
+                    ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_flag, g.error, 1);
+                    if (!ok) break;
+                    armed &= ~(1u << stage);
+                    const uint32_t bar = smem_u32(&ctl->full[stage]);
+                    const uint32_t sa = smem_u32(stages + (size_t)stage * g.stage_bytes);
+                    mbar_expect_tx(bar, g.tx_bytes);
+                    tma_load_2d(sa, &map_a, chunk * g.kchunk,
+                                (int)(row0 + (long)(kh - g.ph) * g.wp + (kw - g.pw)), bar);
+                    tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk,
+                                tap * g.ocp16 + nt * g.n_tile, bar);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // Something gave up. Loads already issued still land in this CTA's shared
+                // memory: wait for them (bounded) before the CTA may exit.
+                for (int s = 0; s < kStages; s++)
+                    if (armed & (1u << s)) {
+                        const uint32_t bar = smem_u32(&ctl->full[s]);
+                        const unsigned long long t0 = global_ns();
+                        while (!mbar_try_wait(bar, (armed_parity >> s) & 1u))
+                            if (global_ns() - t0 > kWaitLimitNs) break;
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
+                const int b = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
+                for (int ks = 0; ks < ksteps; ks++) {
+                    ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, g.error, 3);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(stages + (size_t)stage * g.stage_bytes);
+                    const uint64_t hi = (uint64_t)g.desc_hi << 32;
+                    const uint64_t adesc = hi | (uint64_t)(((sa >> 4) & 0x3FFF) | (1u << 16));
+                    const uint64_t bdesc =
+                        hi | (uint64_t)((((sa + g.a_bytes) >> 4) & 0x3FFF) | (1u << 16));
+                    const int kk = g.kchunk >> 5;
+                    for (int k = 0; k < kk; k++)
+                        tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
+                                  g.idesc, (ks | k) != 0);
+                    tc_commit(smem_u32(&ctl->empty[stage]));
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(smem_u32(&ctl->acc_full[b]));
+            }
+            if (!ok) {
+                // Let every MMA already issued finish before tensor memory is released.
+                tc_commit(smem_u32(&ctl->drain));
+                const unsigned long long t0 = global_ns();
+                while (!mbar_try_wait(smem_u32(&ctl->drain), 0))
+                    if (global_ns() - t0 > kWaitLimitNs) break;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---- epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32) ----
+        const int quad = warp & 3;
+        const int frame = g.hp * g.wp;
+        const long ohw = (long)g.oh * g.ow;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
+            const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
+            const int b = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            const long q = (long)mt * BM + quad * 32 + lane;
+            const int n = (int)(q / frame);
+            const int rem = (int)(q - (long)n * frame);
+            const int oh = rem / g.wp, ow = rem - oh * g.wp;
+            const bool valid = q < g.q_total && oh < g.oh && ow < g.ow;
+            const int r = oh * g.ow + ow;
+            const long pix = (long)n * ohw + r;
+            const float kk = (valid && !g.sums) ? __ldg(g.kmap + pix) : 0.f;
+            ok = mbar_wait(smem_u32(&ctl->acc_full[b]), acc_phase, abort_flag, g.error, 4);
+            ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
+            const int oc0 = nt * g.n_tile;
+            for (int c0 = 0; c0 < g.n_tile; c0 += 16) {
+                uint32_t v[16];
+                tc_ld16(taddr + (uint32_t)c0, v);
+                tc_wait_ld();
+                if (valid) {
+                    if (g.sums) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int oc = oc0 + c0 + j;
+                            if (oc < g.oc)
+                                g.sums[((long)n * g.oc + oc) * ohw + r] = (int)v[j];
+                        }
+                    } else if (g.dst_nhwc) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int oc = oc0 + c0 + j;
+                            if (oc < g.oc)
+                                g.dst[pix * g.oc + oc] = __fmul_rn(
+                                    __fmul_rn((float)(int)v[j], __ldg(g.alpha + oc)), kk);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int oc = oc0 + c0 + j;
+                            if (oc < g.oc)
+                                g.dst[((long)n * g.oc + oc) * ohw + r] = __fmul_rn(
+                                    __fmul_rn((float)(int)v[j], __ldg(g.alpha + oc)), kk);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&ctl->acc_empty[b]));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+                cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+// A [rows][row_bytes] byte matrix, boxes of box_rows x box_bytes, swizzle span = box_bytes.
+bool encode_bytes_2d(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes,
+                     uint32_t box_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapSwizzle sw = box_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                    : CU_TENSOR_MAP_SWIZZLE_32B;
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box,
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *bin_w,
+                                const float *alpha, const float *k, float *dst, int32_t *sums,
+                                int *error_word, cudaStream_t s) {
+    if (p.q_total == 0) return cudaSuccess;
+    CUtensorMap map_a, map_b;
+    if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk, BM) ||
+        !encode_bytes_2d(&map_b, bin_w, (uint64_t)p.kh * p.kw * p.ocp16, (uint64_t)p.icp,
+                         (uint32_t)p.kchunk, (uint32_t)p.n_tile))
+        return cudaErrorNotSupported;
+
+    TcArgs g;
+    g.alpha = alpha; g.kmap = k; g.dst = dst; g.sums = sums; g.error = error_word;
+    g.q_total = p.q_total;
+    g.m_tiles = (int)((p.q_total + BM - 1) / BM);
+    g.n_tiles = p.ocp16 / p.n_tile;
+    g.n_tile = p.n_tile;
+    g.kchunk = p.kchunk; g.chunks_per_tap = p.icp / p.kchunk; g.taps = p.kh * p.kw;
+    g.kw = p.kw; g.ph = p.ph; g.pw = p.pw; g.wp = p.wp; g.hp = p.hp; g.lead = p.lead;
+    g.oh = p.oh; g.ow = p.ow; g.oc = p.oc; g.ocp16 = p.ocp16;
+    g.dst_nhwc = p.dst_nhwc;
+    // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N and M encoded
+    g.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.n_tile >> 3) << 17) |
+              ((uint32_t)(BM >> 4) << 24);
+    // matrix descriptor, upper half: stride between 8-row groups (8 * kchunk bytes, in 16-byte
+    // units), descriptor version 1, swizzle mode
+    const uint32_t sbo = (uint32_t)(8 * p.kchunk) >> 4;
+    const uint32_t layout = p.kchunk == 128 ? 2u : p.kchunk == 64 ? 4u : 6u;
+    g.desc_hi = sbo | (1u << 14) | (layout << 29);
+    g.a_bytes = (uint32_t)(BM * p.kchunk);
+    g.tx_bytes = g.a_bytes + (uint32_t)(p.n_tile * p.kchunk);
+    g.stage_bytes = (g.tx_bytes + 1023u) & ~1023u;
+
+    // At least 120 KB of shared memory so that one CTA owns the SM and all 512 TMEM columns.
+    size_t smem = 2048 + (size_t)kStages * g.stage_bytes;
+    if (smem < 120 * 1024) smem = 120 * 1024;
+    cudaError_t e = cudaFuncSetAttribute(conv_tcgen05_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = g.m_tiles * g.n_tiles;
+    const int grid = tiles < sms ? tiles : sms;
+    conv_tcgen05_kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, g);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace xb200

@@ -40,4 +40,11 @@ cudaError_t launch_conv_popc(const Plan &p, const uint32_t *bin_src, const uint3
                              const float *alpha, const float *k, const int32_t *op_c, float *dst,
                              int32_t *sums, cudaStream_t s);
 
+// The same contract on the tensor cores (tcgen05.mma kind::i8 over +-1 bytes, plan.hpp's framed
+// layout). `error_word` is a device int the kernel sets non-zero if one of its bounded waits
+// ran out; it is never cleared by the kernel.
+cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *bin_w,
+                                const float *alpha, const float *k, float *dst, int32_t *sums,
+                                int *error_word, cudaStream_t s);
+
 }  // namespace xb200

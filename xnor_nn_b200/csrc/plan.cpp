@@ -31,11 +31,12 @@ static Family family_from_env() {
 static bool frame_walk_ok(const Plan &p) {
     return p.sh == 1 && p.sw == 1 && p.oh == p.ih + 2 * p.ph - p.kh + 1 &&
            p.ow == p.iw + 2 * p.pw - p.kw + 1 && p.oh > 0 && p.ow > 0 &&
-           p.kh - 1 - p.ph <= p.ph + p.ih && p.kw - 1 - p.pw <= p.iw;
+           p.kh - 1 - p.ph <= p.ph + p.ih && p.kw - 1 - p.pw <= p.iw &&
+           (long)p.mb * (p.ih + p.ph) * (p.iw + p.pw) < (1L << 30);
 }
 
 // Families whose convolution kernel is compiled into this library.
-static bool family_built(Family f) { return f == kPopc; }
+static bool family_built(Family f) { return f == kPopc || f == kTcgen05; }
 
 void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
     memset(p, 0, sizeof(*p));
