@@ -107,6 +107,91 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
     if (WITH_A) g.a[px] = acc;
 }
 
+// ---- NCHW source, +-1 bytes on the frame: the layout the tensor-core convolution reads -------
+//
+// A block of four warps owns 32 neighbouring pixels and walks the channels in chunks of 64.
+// All warps load (lane = pixel, so a load instruction reads one 128-byte line of a channel
+// plane; 16 independent loads per thread, issued one chunk ahead so that they are in flight
+// while the previous chunk is consumed). |x|/IC goes to a float tile and the sign byte to a byte
+// tile in shared memory. Warp 0 then adds the float tile up channel by channel, one lane per
+// pixel, which keeps upstream's summation order, while the other warps copy the byte tile out
+// as coalesced 64-byte runs per pixel. Blocks are small enough that the whole grid is resident
+// at once for the benchmark layers.
+constexpr int TPX = 32;    // pixels per block
+constexpr int TCC = 64;    // channels per chunk
+constexpr int TLD = TCC + 4;
+constexpr int TWARPS = 4;
+constexpr int TPER = TCC / TWARPS;  // loads per thread and chunk
+
+template <bool WITH_A, bool WITH_PACK>
+__global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const BinArgs g) {
+    __shared__ float f_s[WITH_A ? TCC * TPX : 1];
+    __shared__ __align__(16) uint8_t b_s[WITH_PACK ? TPX * TLD : 4];
+    __shared__ long row_s[TPX];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long px = (long)blockIdx.x * TPX + lane;
+    const bool live = px < g.n_px;
+    const int n = live ? (int)(px / g.hw) : 0;
+    const int r = live ? (int)(px - (long)n * g.hw) : 0;
+    const float *p = g.src + n * g.img_stride + r;
+    if (warp == 0) row_s[lane] = live ? packed_row<kBytesFramed>(g, px) : -1;
+
+    const int c_end = WITH_PACK ? g.words * 4 : g.ic;  // channel extent walked
+    float acc = 0.f;
+    float v[TPER];
+#pragma unroll
+    for (int i = 0; i < TPER; i++) {
+        const int c = warp + TWARPS * i;
+        v[i] = (live && c < g.ic) ? __ldg(p + (long)c * g.hw) : 0.f;
+    }
+    for (int c0 = 0; c0 < c_end; c0 += TCC) {
+#pragma unroll
+        for (int i = 0; i < TPER; i++) {
+            const int cl = warp + TWARPS * i;
+            if (WITH_A) f_s[cl * TPX + lane] = __fmul_rn(fabsf(v[i]), g.inv_ic);
+            if (WITH_PACK)
+                b_s[lane * TLD + cl] = (c0 + cl < g.ic) ? (sign_clear(v[i]) ? 0x01 : 0xFF) : 0x00;
+        }
+        __syncthreads();
+        if (c0 + TCC < c_end) {  // next chunk's loads fly while this one is consumed
+#pragma unroll
+            for (int i = 0; i < TPER; i++) {
+                const int c = c0 + TCC + warp + TWARPS * i;
+                v[i] = (live && c < g.ic) ? __ldg(p + (long)c * g.hw) : 0.f;
+            }
+        }
+        if (WITH_A && warp == 0) {
+            const int nc = min(TCC, g.ic - c0);
+            if (nc == TCC) {
+#pragma unroll
+                for (int j0 = 0; j0 < TCC; j0 += 16) {
+                    float t[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
+                }
+            } else {
+                for (int j = 0; j < nc; j++) acc = __fadd_rn(acc, f_s[j * TPX + lane]);
+            }
+        } else if (WITH_PACK) {
+            // a warp writes two pixels per pass: 16 lanes x 4 bytes each
+            const int first = WITH_A ? warp - 1 : warp, step = WITH_A ? TWARPS - 1 : TWARPS;
+            const int nwords = min(TCC, c_end - c0) / 4;
+            const int half = lane >> 4, wl = lane & 15;
+            for (int pi = 2 * first + half; pi < TPX; pi += 2 * step) {
+                const long row = row_s[pi];
+                if (row >= 0 && wl < nwords)
+                    ((uint32_t *)g.out)[row * g.words + c0 / 4 + wl] =
+                        *reinterpret_cast<const uint32_t *>(&b_s[pi * TLD + 4 * wl]);
+            }
+        }
+        __syncthreads();
+    }
+    if (WITH_A && warp == 0 && live) g.a[px] = acc;
+}
+
 struct BoxArgs {
     const float *a;
     float *k;
@@ -155,6 +240,12 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
     const int threads = 128;
     const unsigned blocks = (unsigned)((g.n_px + threads - 1) / threads);
     if (blocks == 0) return cudaSuccess;
+    if (!p.src_nhwc && (p.family == kTcgen05 || !WITH_PACK)) {
+        binarize_bytes_nchw_kernel<WITH_A, WITH_PACK>
+            <<<(unsigned)((g.n_px + TPX - 1) / TPX), TWARPS * 32, 0, s>>>(g);
+        note_launch();
+        return cudaGetLastError();
+    }
     switch (p.family) {
         case kPopc: binarize_kernel<kBitsDense, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
         case kMmaB1: binarize_kernel<kBitsFramed, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;

@@ -17,7 +17,7 @@
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma.kind::i8 (M=128, N<=256,
 //               K=32 per instruction) from the stages into one of two accumulators in tensor
 //               memory, and tcgen05.commit hands stages back / accumulators on
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (a warp owns 32 TMEM lanes = 32 positions),
+//   warps 2-17  epilogue: tcgen05.ld the accumulator (a warp owns 32 TMEM lanes = 32 positions),
 //               scale by alpha[filter] * K[position] in upstream's order and store; runs under
 //               the next tile's MMAs thanks to the second accumulator
 //
@@ -25,6 +25,7 @@
 // in *error, every role winds down, copies in flight are waited for (again bounded), tensor
 // memory is released and the kernel returns.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "kernels.cuh"
 
@@ -34,7 +35,8 @@ namespace {
 
 constexpr int BM = 128;            // positions per tile = UMMA M = TMEM lanes
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 16;       // epilogue warps: 4 TMEM lane quadrants x column groups
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
@@ -52,6 +54,7 @@ struct TcArgs {
     uint32_t desc_hi;  // upper 32 bits of the shared-memory matrix descriptors
     uint32_t a_bytes, stage_bytes, tx_bytes;
     int dst_nhwc;
+    int debug;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -158,7 +161,9 @@ __device__ __forceinline__ void tc_wait_ld() {
 
 // ---- the kernel --------------------------------------------------------------------------------
 
-struct __align__(8) Control {
+constexpr int kAlphaSmem = 2048;  // filters whose alpha is staged in shared memory
+
+struct __align__(16) Control {
     unsigned long long full[kStages];
     unsigned long long empty[kStages];
     unsigned long long acc_full[2];
@@ -166,8 +171,25 @@ struct __align__(8) Control {
     unsigned long long drain;
     uint32_t tmem_base;
     int abort_flag;
+    float alpha[kAlphaSmem];
 };
+constexpr int kControlBytes = (sizeof(Control) + 1023) / 1024 * 1024;
 
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+
+// KK = tcgen05.mma instructions per pipeline stage (kchunk / 32).
+template <int KK>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
@@ -175,7 +197,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     // stages need the swizzle atom's alignment (1024 B); the control block sits in front
     uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Control *ctl = (Control *)base;
-    uint8_t *stages = base + 1024;
+    uint8_t *stages = base + kControlBytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *abort_flag = &ctl->abort_flag;
@@ -187,7 +209,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(smem_u32(&ctl->acc_full[b]), 1);
-            mbar_init(smem_u32(&ctl->acc_empty[b]), 128);
+            mbar_init(smem_u32(&ctl->acc_empty[b]), 32 * kEpiWarps);
         }
         mbar_init(smem_u32(&ctl->drain), 1);
         ctl->abort_flag = 0;
@@ -199,6 +221,10 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
+    if (alpha_in_smem)
+        for (int i = threadIdx.x; i < g.ocp16; i += kThreads)
+            ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -206,6 +232,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
     const int total_tiles = g.m_tiles * g.n_tiles;
     const int ksteps = g.taps * g.chunks_per_tap;
+    const uint32_t stage0 = smem_u32(stages);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -217,24 +244,34 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
-                const long row0 = (long)g.lead + (long)mt * BM;
+                int row = g.lead + mt * BM - g.ph * g.wp - g.pw;  // tap (0,0)
+                int brow = nt * g.n_tile;
+                int kw = 0, chunk = 0;
                 for (int ks = 0; ks < ksteps; ks++) {
-                    const int tap = ks / g.chunks_per_tap;
-                    const int chunk = ks - tap * g.chunks_per_tap;
-                    const int kh = tap / g.kw, kw = tap - kh * g.kw;
-                    ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_flag, g.error, 1);
-                    if (!ok) break;
+                    const uint32_t ebar = smem_u32(&ctl->empty[stage]);
+                    if (!mbar_try_wait(ebar, phase ^ 1)) {
+                        ok = mbar_wait(ebar, phase ^ 1, abort_flag, g.error, 1);
+                        if (!ok) break;
+                    }
                     armed &= ~(1u << stage);
                     const uint32_t bar = smem_u32(&ctl->full[stage]);
-                    const uint32_t sa = smem_u32(stages + (size_t)stage * g.stage_bytes);
-                    mbar_expect_tx(bar, g.tx_bytes);
-                    tma_load_2d(sa, &map_a, chunk * g.kchunk,
-                                (int)(row0 + (long)(kh - g.ph) * g.wp + (kw - g.pw)), bar);
-                    tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk,
-                                tap * g.ocp16 + nt * g.n_tile, bar);
-                    armed |= 1u << stage;
-                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    const uint32_t sa = stage0 + (uint32_t)stage * g.stage_bytes;
+                    if (g.debug & 1) {
+                        mbar_arrive(bar);
+                    } else {
+                        mbar_expect_tx(bar, g.tx_bytes);
+                        tma_load_2d(sa, &map_a, chunk * g.kchunk, row, bar);
+                        tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
+                        armed |= 1u << stage;
+                        armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (++chunk == g.chunks_per_tap) {  // next filter tap
+                        chunk = 0;
+                        brow += g.ocp16;
+                        if (++kw == g.kw) { kw = 0; row += g.wp - (g.kw - 1); }
+                        else row += 1;
+                    }
                 }
             }
             if (!ok) {
@@ -251,11 +288,15 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- MMA issuer ----
+            // ---- MMA issuer: kept lean, a single thread feeds the tensor pipe ----
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
             bool ok = true;
+            const uint64_t hi = (uint64_t)g.desc_hi << 32;
+            const uint32_t a_lo0 = ((stage0 >> 4) & 0x3FFF) | (1u << 16);
+            const uint32_t b_lo0 = (((stage0 + g.a_bytes) >> 4) & 0x3FFF) | (1u << 16);
+            const uint32_t stage_units = g.stage_bytes >> 4;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
                 const int b = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
@@ -263,19 +304,22 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
+                uint32_t accumulate = 0;
                 for (int ks = 0; ks < ksteps; ks++) {
-                    ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, g.error, 3);
-                    if (!ok) break;
+                    const uint32_t fbar = smem_u32(&ctl->full[stage]);
+                    if (!mbar_try_wait(fbar, phase)) {
+                        ok = mbar_wait(fbar, phase, abort_flag, g.error, 3);
+                        if (!ok) break;
+                    }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(stages + (size_t)stage * g.stage_bytes);
-                    const uint64_t hi = (uint64_t)g.desc_hi << 32;
-                    const uint64_t adesc = hi | (uint64_t)(((sa >> 4) & 0x3FFF) | (1u << 16));
-                    const uint64_t bdesc =
-                        hi | (uint64_t)((((sa + g.a_bytes) >> 4) & 0x3FFF) | (1u << 16));
-                    const int kk = g.kchunk >> 5;
-                    for (int k = 0; k < kk; k++)
+                    const uint64_t adesc = hi | (uint64_t)(a_lo0 + (uint32_t)stage * stage_units);
+                    const uint64_t bdesc = hi | (uint64_t)(b_lo0 + (uint32_t)stage * stage_units);
+#pragma unroll
+                    for (int k = 0; k < KK; k++) {
                         tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
-                                  g.idesc, (ks | k) != 0);
+                                  g.idesc, k == 0 ? accumulate : 1u);
+                    }
+                    accumulate = 1;
                     tc_commit(smem_u32(&ctl->empty[stage]));
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
@@ -292,7 +336,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         __syncwarp();
     } else {
         // ---- epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32) ----
+        // Several warps share a quadrant and split its columns between them.
         const int quad = warp & 3;
+        const int cgroup = (warp - 2) >> 2, cgroups = kEpiWarps / 4;
         const int frame = g.hp * g.wp;
         const long ohw = (long)g.oh * g.ow;
         int it = 0;
@@ -309,39 +355,53 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             const int r = oh * g.ow + ow;
             const long pix = (long)n * ohw + r;
             const float kk = (valid && !g.sums) ? __ldg(g.kmap + pix) : 0.f;
+            const int oc0 = nt * g.n_tile;
+            const int n_valid = min(g.n_tile, g.oc - oc0);  // real filters in this tile
             ok = mbar_wait(smem_u32(&ctl->acc_full[b]), acc_phase, abort_flag, g.error, 4);
             ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
-            const int oc0 = nt * g.n_tile;
-            for (int c0 = 0; c0 < g.n_tile; c0 += 16) {
-                uint32_t v[16];
-                tc_ld16(taddr + (uint32_t)c0, v);
-                tc_wait_ld();
-                if (valid) {
-                    if (g.sums) {
+            if (!g.sums && !g.dst_nhwc && !(g.debug & 2)) {
+                // NCHW floats: for one filter the 32 lanes hold 32 neighbouring pixels, so a
+                // store instruction writes one contiguous run.
+                float *out = g.dst + ((long)n * g.oc + oc0) * ohw + r;
+                const float *al = alpha_in_smem ? ctl->alpha + oc0 : g.alpha + oc0;
+                for (int c0 = 32 * cgroup; c0 < g.n_tile; c0 += 32 * cgroups) {
+                    uint32_t v[32];
+                    if (c0 + 32 <= g.n_tile) {
+                        tc_ld32(taddr + (uint32_t)c0, v);
+                    } else {  // N is a multiple of 16, not always of 32
+                        tc_ld16(taddr + (uint32_t)c0, v);
+                    }
+                    tc_wait_ld();
+                    if (valid) {
+                        const int lim = n_valid - c0;
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < lim)
+                                out[(long)(c0 + j) * ohw] =
+                                    __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk);
+                    }
+                }
+            } else {
+                for (int c0 = 16 * cgroup; c0 < g.n_tile; c0 += 16 * cgroups) {
+                    uint32_t v[16];
+                    tc_ld16(taddr + (uint32_t)c0, v);
+                    tc_wait_ld();
+                    if (valid && !(g.debug & 2)) {
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
                             const int oc = oc0 + c0 + j;
-                            if (oc < g.oc)
+                            if (oc >= g.oc) continue;
+                            if (g.sums) {
                                 g.sums[((long)n * g.oc + oc) * ohw + r] = (int)v[j];
-                        }
-                    } else if (g.dst_nhwc) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int oc = oc0 + c0 + j;
-                            if (oc < g.oc)
-                                g.dst[pix * g.oc + oc] = __fmul_rn(
-                                    __fmul_rn((float)(int)v[j], __ldg(g.alpha + oc)), kk);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int oc = oc0 + c0 + j;
-                            if (oc < g.oc)
-                                g.dst[((long)n * g.oc + oc) * ohw + r] = __fmul_rn(
-                                    __fmul_rn((float)(int)v[j], __ldg(g.alpha + oc)), kk);
+                            } else {
+                                const float x =
+                                    __fmul_rn(__fmul_rn((float)(int)v[j], __ldg(g.alpha + oc)), kk);
+                                if (g.dst_nhwc) g.dst[pix * g.oc + oc] = x;
+                                else g.dst[((long)n * g.oc + oc) * ohw + r] = x;
+                            }
                         }
                     }
                 }
@@ -419,6 +479,7 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.kw = p.kw; g.ph = p.ph; g.pw = p.pw; g.wp = p.wp; g.hp = p.hp; g.lead = p.lead;
     g.oh = p.oh; g.ow = p.ow; g.oc = p.oc; g.ocp16 = p.ocp16;
     g.dst_nhwc = p.dst_nhwc;
+    { const char *e = getenv("XNOR_NN_B200_DEBUG"); g.debug = e ? atoi(e) : 0; }
     // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N and M encoded
     g.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.n_tile >> 3) << 17) |
               ((uint32_t)(BM >> 4) << 24);
@@ -432,17 +493,20 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.stage_bytes = (g.tx_bytes + 1023u) & ~1023u;
 
     // At least 120 KB of shared memory so that one CTA owns the SM and all 512 TMEM columns.
-    size_t smem = 2048 + (size_t)kStages * g.stage_bytes;
+    size_t smem = 1024 + kControlBytes + (size_t)kStages * g.stage_bytes;
     if (smem < 120 * 1024) smem = 120 * 1024;
-    cudaError_t e = cudaFuncSetAttribute(conv_tcgen05_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    auto kernel = p.kchunk == 128 ? conv_tcgen05_kernel<4>
+                  : p.kchunk == 64 ? conv_tcgen05_kernel<2>
+                                   : conv_tcgen05_kernel<1>;
+    cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles = g.m_tiles * g.n_tiles;
     const int grid = tiles < sms ? tiles : sms;
-    conv_tcgen05_kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, g);
+    kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, g);
     note_launch();
     return cudaGetLastError();
 }
