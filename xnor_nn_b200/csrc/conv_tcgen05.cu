@@ -11,15 +11,25 @@
 // shift, so the A tile of a tap is a plain 2-D TMA box at a shifted row; no im2col buffer exists.
 // Positions on the frame border are computed and dropped by the epilogue.
 //
-// One CTA per SM, persistent over (position tile, filter tile) pairs, 192 threads:
-//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, no multicast) into a ring of
-//               shared-memory stages; completion is counted on an mbarrier per stage
+// One CTA per SM, persistent over (position tile, filter tile) pairs:
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, no multicast) into rings of
+//               shared-memory buffers; completion is counted on an mbarrier per buffer
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma.kind::i8 (M=128, N<=256,
-//               K=32 per instruction) from the stages into one of two accumulators in tensor
-//               memory, and tcgen05.commit hands stages back / accumulators on
-//   warps 2-17  epilogue: tcgen05.ld the accumulator (a warp owns 32 TMEM lanes = 32 positions),
-//               scale by alpha[filter] * K[position] in upstream's order and store; runs under
-//               the next tile's MMAs thanks to the second accumulator
+//               K=32 per instruction) into one of two accumulators in tensor memory, and
+//               tcgen05.commit hands buffers back / accumulators on
+//   warps 2-17  epilogue: tcgen05.ld the accumulator (a warp owns 32 TMEM lanes = 32 positions
+//               and a share of the columns), scale by alpha[filter] * K[position] in upstream's
+//               order and store; runs under the next tile's MMAs thanks to the second
+//               accumulator
+//
+// Two kernels share these roles. The slab kernel is the fast one: the nine (or KH*KW) shifted A
+// tiles of a position tile overlap almost entirely, so it loads the union once per channel
+// chunk (128 + (KH-1)*(IW+PW) + KW-1 rows, a "slab") and points each tap's matrix descriptor at
+// a row offset inside it (the swizzle is a function of the absolute shared-memory address, so a
+// descriptor may start at any row). Only the weights are streamed per tap, which cuts the
+// L2->shared traffic per tile by a third and leaves room for a deeper weight ring; with 48 KB
+// stages the ring was too shallow to cover the TMA latency. The per-tap kernel loads an A tile
+// per tap and serves the shapes whose slab does not fit.
 //
 // Every wait on an mbarrier is bounded in time: when the bound is hit the kernel records where
 // in *error, every role winds down, copies in flight are waited for (again bounded), tensor
@@ -55,6 +65,14 @@ struct TcArgs {
     uint32_t a_bytes, stage_bytes, tx_bytes;
     int dst_nhwc;
     int debug;
+    // slab kernel only
+    int group;            // channel chunks per weight stage (G)
+    int groups_per_tile;  // chunks_per_tap / G
+    int slab_rows;        // rows of a slab, multiple of 8, <= 256
+    int n_slabs;          // slab-ring depth, counted in groups
+    int n_ring;           // weight-ring depth
+    uint32_t slab_chunk_bytes, slab_group_bytes, b_chunk_bytes, b_stage_bytes;
+    uint32_t slab_tx_bytes, b_tx_bytes;  // bytes TMA writes per group / stage (the boxes)
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -163,9 +181,14 @@ __device__ __forceinline__ void tc_wait_ld() {
 
 constexpr int kAlphaSmem = 2048;  // filters whose alpha is staged in shared memory
 
+constexpr int kMaxRing = 8;   // weight-ring depth limit of the slab kernel
+constexpr int kMaxSlabs = 8;  // slab-ring depth limit
+
 struct __align__(16) Control {
-    unsigned long long full[kStages];
-    unsigned long long empty[kStages];
+    unsigned long long full[kMaxRing];
+    unsigned long long empty[kMaxRing];
+    unsigned long long slab_full[kMaxSlabs];
+    unsigned long long slab_empty[kMaxSlabs];
     unsigned long long acc_full[2];
     unsigned long long acc_empty[2];
     unsigned long long drain;
@@ -186,6 +209,88 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *v) {
           "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
           "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr));
+}
+
+// ---- epilogue role (both kernels) ----------------------------------------------------------------
+// Warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); several warps share a quadrant and split
+// its columns between them.
+__device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uint32_t tmem_base,
+                                              int warp, int lane, bool alpha_in_smem) {
+    volatile int *abort_flag = &ctl->abort_flag;
+    const int total_tiles = g.m_tiles * g.n_tiles;
+    // Several warps share a quadrant and split its columns between them.
+    const int quad = warp & 3;
+    const int cgroup = (warp - 2) >> 2, cgroups = kEpiWarps / 4;
+    const int frame = g.hp * g.wp;
+    const long ohw = (long)g.oh * g.ow;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
+        const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
+        const int b = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        const long q = (long)mt * BM + quad * 32 + lane;
+        const int n = (int)(q / frame);
+        const int rem = (int)(q - (long)n * frame);
+        const int oh = rem / g.wp, ow = rem - oh * g.wp;
+        const bool valid = q < g.q_total && oh < g.oh && ow < g.ow;
+        const int r = oh * g.ow + ow;
+        const long pix = (long)n * ohw + r;
+        const float kk = (valid && !g.sums) ? __ldg(g.kmap + pix) : 0.f;
+        const int oc0 = nt * g.n_tile;
+        const int n_valid = min(g.n_tile, g.oc - oc0);  // real filters in this tile
+        ok = mbar_wait(smem_u32(&ctl->acc_full[b]), acc_phase, abort_flag, g.error, 4);
+        ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
+        if (!g.sums && !g.dst_nhwc && !(g.debug & 2)) {
+            // NCHW floats: for one filter the 32 lanes hold 32 neighbouring pixels, so a
+            // store instruction writes one contiguous run.
+            float *out = g.dst + ((long)n * g.oc + oc0) * ohw + r;
+            const float *al = alpha_in_smem ? ctl->alpha + oc0 : g.alpha + oc0;
+            for (int c0 = 32 * cgroup; c0 < g.n_tile; c0 += 32 * cgroups) {
+                uint32_t v[32];
+                if (c0 + 32 <= g.n_tile) {
+                    tc_ld32(taddr + (uint32_t)c0, v);
+                } else {  // N is a multiple of 16, not always of 32
+                    tc_ld16(taddr + (uint32_t)c0, v);
+                }
+                tc_wait_ld();
+                if (valid) {
+                    const int lim = n_valid - c0;
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (j < lim)
+                            out[(long)(c0 + j) * ohw] =
+                                __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk);
+                }
+            }
+        } else {
+            for (int c0 = 16 * cgroup; c0 < g.n_tile; c0 += 16 * cgroups) {
+                uint32_t v[16];
+                tc_ld16(taddr + (uint32_t)c0, v);
+                tc_wait_ld();
+                if (valid && !(g.debug & 2)) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int oc = oc0 + c0 + j;
+                        if (oc >= g.oc) continue;
+                        if (g.sums) {
+                            g.sums[((long)n * g.oc + oc) * ohw + r] = (int)v[j];
+                        } else {
+                            const float x =
+                                __fmul_rn(__fmul_rn((float)(int)v[j], __ldg(g.alpha + oc)), kk);
+                            if (g.dst_nhwc) g.dst[pix * g.oc + oc] = x;
+                            else g.dst[((long)n * g.oc + oc) * ohw + r] = x;
+                        }
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctl->acc_empty[b]));
+    }
 }
 
 // KK = tcgen05.mma instructions per pipeline stage (kchunk / 32).
@@ -335,80 +440,210 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         __syncwarp();
     } else {
-        // ---- epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32) ----
-        // Several warps share a quadrant and split its columns between them.
-        const int quad = warp & 3;
-        const int cgroup = (warp - 2) >> 2, cgroups = kEpiWarps / 4;
-        const int frame = g.hp * g.wp;
-        const long ohw = (long)g.oh * g.ow;
-        int it = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
-            const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
-            const int b = it & 1;
-            const uint32_t acc_phase = (it >> 1) & 1;
-            const long q = (long)mt * BM + quad * 32 + lane;
-            const int n = (int)(q / frame);
-            const int rem = (int)(q - (long)n * frame);
-            const int oh = rem / g.wp, ow = rem - oh * g.wp;
-            const bool valid = q < g.q_total && oh < g.oh && ow < g.ow;
-            const int r = oh * g.ow + ow;
-            const long pix = (long)n * ohw + r;
-            const float kk = (valid && !g.sums) ? __ldg(g.kmap + pix) : 0.f;
-            const int oc0 = nt * g.n_tile;
-            const int n_valid = min(g.n_tile, g.oc - oc0);  // real filters in this tile
-            ok = mbar_wait(smem_u32(&ctl->acc_full[b]), acc_phase, abort_flag, g.error, 4);
-            ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
-            if (!g.sums && !g.dst_nhwc && !(g.debug & 2)) {
-                // NCHW floats: for one filter the 32 lanes hold 32 neighbouring pixels, so a
-                // store instruction writes one contiguous run.
-                float *out = g.dst + ((long)n * g.oc + oc0) * ohw + r;
-                const float *al = alpha_in_smem ? ctl->alpha + oc0 : g.alpha + oc0;
-                for (int c0 = 32 * cgroup; c0 < g.n_tile; c0 += 32 * cgroups) {
-                    uint32_t v[32];
-                    if (c0 + 32 <= g.n_tile) {
-                        tc_ld32(taddr + (uint32_t)c0, v);
-                    } else {  // N is a multiple of 16, not always of 32
-                        tc_ld16(taddr + (uint32_t)c0, v);
-                    }
-                    tc_wait_ld();
-                    if (valid) {
-                        const int lim = n_valid - c0;
-#pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (j < lim)
-                                out[(long)(c0 + j) * ohw] =
-                                    __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk);
-                    }
-                }
-            } else {
-                for (int c0 = 16 * cgroup; c0 < g.n_tile; c0 += 16 * cgroups) {
-                    uint32_t v[16];
-                    tc_ld16(taddr + (uint32_t)c0, v);
-                    tc_wait_ld();
-                    if (valid && !(g.debug & 2)) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int oc = oc0 + c0 + j;
-                            if (oc >= g.oc) continue;
-                            if (g.sums) {
-                                g.sums[((long)n * g.oc + oc) * ohw + r] = (int)v[j];
-                            } else {
-                                const float x =
-                                    __fmul_rn(__fmul_rn((float)(int)v[j], __ldg(g.alpha + oc)), kk);
-                                if (g.dst_nhwc) g.dst[pix * g.oc + oc] = x;
-                                else g.dst[((long)n * g.oc + oc) * ohw + r] = x;
-                            }
+        epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---- slab kernel -------------------------------------------------------------------------------
+//
+// K order of a tile: channel-chunk group (outer) x filter tap (inner). A group is G consecutive
+// chunks of kchunk channels; its slab (G buffers of slab_rows x kchunk bytes) stays resident
+// for all taps while the weight ring streams one stage per tap (G boxes of n_tile x kchunk
+// bytes). A stage therefore feeds G*KK tcgen05.mma instructions.
+template <int KK>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
+                         const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Control *ctl = (Control *)base;
+    const uint32_t slab0 = smem_u32(base + kControlBytes);
+    const uint32_t ring0 = slab0 + (uint32_t)g.n_slabs * g.slab_group_bytes;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int *abort_flag = &ctl->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMaxRing; s++) {
+            mbar_init(smem_u32(&ctl->full[s]), 1);
+            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int s = 0; s < kMaxSlabs; s++) {
+            mbar_init(smem_u32(&ctl->slab_full[s]), 1);
+            mbar_init(smem_u32(&ctl->slab_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&ctl->acc_full[b]), 1);
+            mbar_init(smem_u32(&ctl->acc_empty[b]), 32 * kEpiWarps);
+        }
+        mbar_init(smem_u32(&ctl->drain), 1);
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
+    if (alpha_in_smem)
+        for (int i = threadIdx.x; i < g.ocp16; i += kThreads)
+            ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+    const int total_tiles = g.m_tiles * g.n_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            int stage = 0, slab = 0;
+            uint32_t phase = 0, slab_phase = 0;
+            uint32_t armed = 0, armed_parity = 0;            // weight ring
+            uint32_t slab_armed = 0, slab_armed_parity = 0;  // slab ring
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
+                const int row0 = g.lead + mt * BM - g.ph * g.wp - g.pw;  // first slab row
+                for (int cg = 0; ok && cg < g.groups_per_tile; cg++) {
+                    // the slab of this chunk group
+                    {
+                        const uint32_t ebar = smem_u32(&ctl->slab_empty[slab]);
+                        if (!mbar_try_wait(ebar, slab_phase ^ 1)) {
+                            ok = mbar_wait(ebar, slab_phase ^ 1, abort_flag, g.error, 5);
+                            if (!ok) break;
                         }
+                        slab_armed &= ~(1u << slab);
+                        const uint32_t bar = smem_u32(&ctl->slab_full[slab]);
+                        const uint32_t dst = slab0 + (uint32_t)slab * g.slab_group_bytes;
+                        mbar_expect_tx(bar, g.slab_tx_bytes);
+                        for (int c = 0; c < g.group; c++)
+                            tma_load_2d(dst + (uint32_t)c * g.slab_chunk_bytes, &map_a,
+                                        (cg * g.group + c) * g.kchunk, row0, bar);
+                        slab_armed |= 1u << slab;
+                        slab_armed_parity =
+                            (slab_armed_parity & ~(1u << slab)) | (slab_phase << slab);
+                        if (++slab == g.n_slabs) { slab = 0; slab_phase ^= 1; }
+                    }
+                    // one weight stage per tap
+                    int brow = nt * g.n_tile;
+                    for (int t = 0; t < g.taps; t++, brow += g.ocp16) {
+                        const uint32_t ebar = smem_u32(&ctl->empty[stage]);
+                        if (!mbar_try_wait(ebar, phase ^ 1)) {
+                            ok = mbar_wait(ebar, phase ^ 1, abort_flag, g.error, 1);
+                            if (!ok) break;
+                        }
+                        armed &= ~(1u << stage);
+                        const uint32_t bar = smem_u32(&ctl->full[stage]);
+                        const uint32_t dst = ring0 + (uint32_t)stage * g.b_stage_bytes;
+                        mbar_expect_tx(bar, g.b_tx_bytes);
+                        for (int c = 0; c < g.group; c++)
+                            tma_load_2d(dst + (uint32_t)c * g.b_chunk_bytes, &map_b,
+                                        (cg * g.group + c) * g.kchunk, brow, bar);
+                        armed |= 1u << stage;
+                        armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                        if (++stage == g.n_ring) { stage = 0; phase ^= 1; }
                     }
                 }
             }
-            tc_fence_before();
-            mbar_arrive(smem_u32(&ctl->acc_empty[b]));
+            if (!ok) {
+                // Loads already issued still land in this CTA's shared memory: wait for them
+                // (bounded) before the CTA may exit.
+                for (int s = 0; s < kMaxRing; s++)
+                    if (armed & (1u << s)) {
+                        const unsigned long long t0 = global_ns();
+                        while (!mbar_try_wait(smem_u32(&ctl->full[s]), (armed_parity >> s) & 1u))
+                            if (global_ns() - t0 > kWaitLimitNs) break;
+                    }
+                for (int s = 0; s < kMaxSlabs; s++)
+                    if (slab_armed & (1u << s)) {
+                        const unsigned long long t0 = global_ns();
+                        while (!mbar_try_wait(smem_u32(&ctl->slab_full[s]),
+                                              (slab_armed_parity >> s) & 1u))
+                            if (global_ns() - t0 > kWaitLimitNs) break;
+                    }
+            }
         }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            int stage = 0, slab = 0;
+            uint32_t phase = 0, slab_phase = 0;
+            int it = 0;
+            bool ok = true;
+            const uint64_t hi = (uint64_t)g.desc_hi << 32;
+            const uint32_t a_lo0 = ((slab0 >> 4) & 0x3FFF) | (1u << 16);
+            const uint32_t b_lo0 = ((ring0 >> 4) & 0x3FFF) | (1u << 16);
+            const uint32_t row_units = (uint32_t)g.kchunk >> 4;  // one slab row, 16-byte units
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
+                const int b = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
+                uint32_t accumulate = 0;
+                for (int cg = 0; ok && cg < g.groups_per_tile; cg++) {
+                    const uint32_t sbar = smem_u32(&ctl->slab_full[slab]);
+                    if (!mbar_try_wait(sbar, slab_phase)) {
+                        ok = mbar_wait(sbar, slab_phase, abort_flag, g.error, 6);
+                        if (!ok) break;
+                    }
+                    const uint32_t a_slab = a_lo0 + (uint32_t)slab * (g.slab_group_bytes >> 4);
+                    uint32_t a_tap = a_slab;  // descriptor of tap (0,0): slab row 0
+                    int kw = 0;
+                    for (int t = 0; t < g.taps; t++) {
+                        const uint32_t fbar = smem_u32(&ctl->full[stage]);
+                        if (!mbar_try_wait(fbar, phase)) {
+                            ok = mbar_wait(fbar, phase, abort_flag, g.error, 3);
+                            if (!ok) break;
+                        }
+                        tc_fence_after();
+                        const uint32_t b_lo = b_lo0 + (uint32_t)stage * (g.b_stage_bytes >> 4);
+                        for (int c = 0; c < g.group; c++) {
+                            const uint64_t adesc = hi | (uint64_t)(a_tap + (uint32_t)c * (g.slab_chunk_bytes >> 4));
+                            const uint64_t bdesc = hi | (uint64_t)(b_lo + (uint32_t)c * (g.b_chunk_bytes >> 4));
+#pragma unroll
+                            for (int k = 0; k < KK; k++) {
+                                tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k),
+                                          bdesc + (uint64_t)(2 * k), g.idesc,
+                                          (k == 0 && c == 0) ? accumulate : 1u);
+                            }
+                        }
+                        accumulate = 1;
+                        tc_commit(smem_u32(&ctl->empty[stage]));
+                        if (++stage == g.n_ring) { stage = 0; phase ^= 1; }
+                        // next tap: one position to the right, or down to the next frame row
+                        if (++kw == g.kw) { kw = 0; a_tap += (uint32_t)(g.wp - (g.kw - 1)) * row_units; }
+                        else a_tap += row_units;
+                    }
+                    if (ok) tc_commit(smem_u32(&ctl->slab_empty[slab]));
+                    if (++slab == g.n_slabs) { slab = 0; slab_phase ^= 1; }
+                }
+                if (ok) tc_commit(smem_u32(&ctl->acc_full[b]));
+            }
+            if (!ok) {
+                // Let every MMA already issued finish before tensor memory is released.
+                tc_commit(smem_u32(&ctl->drain));
+                const unsigned long long t0 = global_ns();
+                while (!mbar_try_wait(smem_u32(&ctl->drain), 0))
+                    if (global_ns() - t0 > kWaitLimitNs) break;
+            }
+        }
+        __syncwarp();
+    } else {
+        epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
     tc_fence_before();
@@ -492,14 +727,56 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.tx_bytes = g.a_bytes + (uint32_t)(p.n_tile * p.kchunk);
     g.stage_bytes = (g.tx_bytes + 1023u) & ~1023u;
 
+    const size_t smem_limit = 227 * 1024;
+    const int kk = p.kchunk / 32;
+    // Slab geometry: rows a tile touches over all taps, and how many chunks share a weight stage.
+    const int slab_rows = (BM + (p.kh - 1) * p.wp + (p.kw - 1) + 7) & ~7;
+    int group = 1;
+    for (int cand = g.chunks_per_tap; cand >= 1; cand--)
+        if (g.chunks_per_tap % cand == 0 && cand * kk <= 6) { group = cand; break; }
+    g.group = group;
+    g.groups_per_tile = g.chunks_per_tap / group;
+    g.slab_rows = slab_rows;
+    g.slab_chunk_bytes = (uint32_t)(slab_rows * p.kchunk + 1023) & ~1023u;
+    g.slab_group_bytes = g.slab_chunk_bytes * (uint32_t)group;
+    g.b_chunk_bytes = (uint32_t)(p.n_tile * p.kchunk + 1023) & ~1023u;
+    g.b_stage_bytes = g.b_chunk_bytes * (uint32_t)group;
+    g.slab_tx_bytes = (uint32_t)(group * slab_rows * p.kchunk);
+    g.b_tx_bytes = (uint32_t)(group * p.n_tile * p.kchunk);
+    // Two slab buffers: the next group's slab loads while the current one is in use (a group
+    // lasts KH*KW stages, far longer than a load). The rest of shared memory is weight ring.
+    const size_t fixed = 1024 + kControlBytes;
+    const int n_slabs = 2;
+    long ring = ((long)smem_limit - (long)fixed - (long)n_slabs * g.slab_group_bytes) /
+                (long)g.b_stage_bytes;
+    if (ring > kMaxRing) ring = kMaxRing;
+    g.n_slabs = n_slabs;
+    g.n_ring = (int)ring;
+    // The slab kernel wins where it packs more MMAs into a weight stage than the per-tap kernel
+    // can (measured: 93 vs 131 us on the 5x5 / 96-channel layer); with a single chunk per stage
+    // the per-tap kernel is a little faster (39 vs 43 us on conv4).
+    const bool use_slab = slab_rows <= 256 && ring >= 3 && (group > 1 || (g.debug & 2048)) && !(g.debug & 1024);
+
+    cudaError_t e;
+    size_t smem;
+    void (*kernel)(CUtensorMap, CUtensorMap, TcArgs);
+    if (use_slab) {
+        if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk,
+                             (uint32_t)slab_rows))
+            return cudaErrorNotSupported;
+        smem = fixed + (size_t)n_slabs * g.slab_group_bytes + (size_t)g.n_ring * g.b_stage_bytes;
+        kernel = kk == 4 ? conv_tcgen05_slab_kernel<4>
+                 : kk == 2 ? conv_tcgen05_slab_kernel<2>
+                           : conv_tcgen05_slab_kernel<1>;
+    } else {
+        smem = fixed + (size_t)kStages * g.stage_bytes;
+        kernel = kk == 4 ? conv_tcgen05_kernel<4>
+                 : kk == 2 ? conv_tcgen05_kernel<2>
+                           : conv_tcgen05_kernel<1>;
+    }
     // At least 120 KB of shared memory so that one CTA owns the SM and all 512 TMEM columns.
-    size_t smem = 1024 + kControlBytes + (size_t)kStages * g.stage_bytes;
     if (smem < 120 * 1024) smem = 120 * 1024;
-    auto kernel = p.kchunk == 128 ? conv_tcgen05_kernel<4>
-                  : p.kchunk == 64 ? conv_tcgen05_kernel<2>
-                                   : conv_tcgen05_kernel<1>;
-    cudaError_t e =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
     if (e != cudaSuccess) return e;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
