@@ -109,16 +109,16 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 
 // ---- NCHW source, +-1 bytes on the frame: the layout the tensor-core convolution reads -------
 //
-// A block of four warps owns 32 neighbouring pixels and walks the channels in chunks of 64.
+// A block of four warps owns 32 neighbouring pixels and walks the channels in chunks of 128.
 // All warps load (lane = pixel, so a load instruction reads one 128-byte line of a channel
-// plane; 16 independent loads per thread, issued one chunk ahead so that they are in flight
+// plane; 32 independent loads per thread, issued one chunk ahead so that they are in flight
 // while the previous chunk is consumed). |x|/IC goes to a float tile and the sign byte to a byte
 // tile in shared memory. Warp 0 then adds the float tile up channel by channel, one lane per
 // pixel, which keeps upstream's summation order, while the other warps copy the byte tile out
-// as coalesced 64-byte runs per pixel. Blocks are small enough that the whole grid is resident
+// as one coalesced 128-byte line per pixel. Blocks are small enough that the whole grid is resident
 // at once for the benchmark layers.
 constexpr int TPX = 32;    // pixels per block
-constexpr int TCC = 64;    // channels per chunk
+constexpr int TCC = 128;   // channels per chunk
 constexpr int TLD = TCC + 4;
 constexpr int TWARPS = 4;
 constexpr int TPER = TCC / TWARPS;  // loads per thread and chunk
@@ -176,11 +176,13 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
                 for (int j = 0; j < nc; j++) acc = __fadd_rn(acc, f_s[j * TPX + lane]);
             }
         } else if (WITH_PACK) {
-            // a warp writes two pixels per pass: 16 lanes x 4 bytes each
+            // a warp writes one pixel per pass: 32 lanes x 4 bytes, one 128-byte line
             const int first = WITH_A ? warp - 1 : warp, step = WITH_A ? TWARPS - 1 : TWARPS;
             const int nwords = min(TCC, c_end - c0) / 4;
-            const int half = lane >> 4, wl = lane & 15;
-            for (int pi = 2 * first + half; pi < TPX; pi += 2 * step) {
+            constexpr int WPP = TCC / 4;   // 32-bit words per pixel and chunk
+            constexpr int PPW = 32 / WPP;  // pixels a warp writes per pass
+            const int half = lane / WPP, wl = lane % WPP;
+            for (int pi = PPW * first + half; pi < TPX; pi += PPW * step) {
                 const long row = row_s[pi];
                 if (row >= 0 && wl < nwords)
                     ((uint32_t *)g.out)[row * g.words + c0 / 4 + wl] =
