@@ -218,8 +218,9 @@ xnor_nn_status_t exec_calculate_k(const xnor_nn_convolution_t *c, xnor_nn_resour
     return xnor_nn_success;
 }
 
+// fuse_k: the tensor-core epilogue derives K from A itself (the caller skipped the stencil).
 xnor_nn_status_t run_conv(const Plan &p, ResCtx *x, xnor_nn_resources_t res, float *dst,
-                          int32_t *sums) {
+                          int32_t *sums, bool fuse_k = false) {
     switch (p.family) {
         case kPopc:
             CU(launch_conv_popc(p, (const uint32_t *)res[xnor_nn_resource_bin_src],
@@ -233,8 +234,10 @@ xnor_nn_status_t run_conv(const Plan &p, ResCtx *x, xnor_nn_resources_t res, flo
             CU(launch_conv_tcgen05(p, res[xnor_nn_resource_bin_src],
                                    res[xnor_nn_resource_bin_weights],
                                    (const float *)res[xnor_nn_resource_alpha],
-                                   (const float *)res[xnor_nn_resource_k], dst, sums,
-                                   x->error_word, x->stream));
+                                   fuse_k ? nullptr : (const float *)res[xnor_nn_resource_k],
+                                   (const float *)res[xnor_nn_resource_a],
+                                   (float *)res[xnor_nn_resource_k], dst, sums, x->error_word,
+                                   x->stream));
             return xnor_nn_success;
         default:
             snprintf(t_last_error, sizeof t_last_error, "kernel family %s is not built in",
@@ -467,9 +470,11 @@ xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_re
     }
     CU(launch_binarize_data(*p, (const float *)src, res[xnor_nn_resource_bin_src],
                             (float *)res[xnor_nn_resource_a], x->stream));
-    CU(launch_box_filter(*p, (const float *)res[xnor_nn_resource_a],
-                         (float *)res[xnor_nn_resource_k], x->stream));
-    st = run_conv(*p, x, res, dst, nullptr);
+    const bool fuse_k = p->family == kTcgen05;
+    if (!fuse_k)
+        CU(launch_box_filter(*p, (const float *)res[xnor_nn_resource_a],
+                             (float *)res[xnor_nn_resource_k], x->stream));
+    st = run_conv(*p, x, res, dst, nullptr, fuse_k);
     if (st != xnor_nn_success) return st;
     if (!direct)
         CU(cudaMemcpyAsync(user, dst, dst_elems(*p) * sizeof(float), cudaMemcpyDeviceToHost,

@@ -52,7 +52,11 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct TcArgs {
     const float *alpha;
-    const float *kmap;
+    const float *kmap;   // K per output pixel, or null: box-filter it from amap in the epilogue
+    const float *amap;   // mean |x| per input pixel (used when kmap is null)
+    float *kmap_out;     // where the epilogue records the K it computed (may be null)
+    float inv_khw;
+    int ih, iw, kh;
     float *dst;
     int32_t *sums;
     int *error;
@@ -236,7 +240,26 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
         const bool valid = q < g.q_total && oh < g.oh && ow < g.ow;
         const int r = oh * g.ow + ow;
         const long pix = (long)n * ohw + r;
-        const float kk = (valid && !g.sums) ? __ldg(g.kmap + pix) : 0.f;
+        float kk = 0.f;
+        if (valid && !g.sums) {
+            if (g.kmap) {
+                kk = __ldg(g.kmap + pix);
+            } else {
+                // K = box filter of A over the taps inside the image, each term scaled by
+                // 1/(KH*KW), added in upstream's tap order (src/bcast_calculate_k.cpp:69-85)
+                const float *img = g.amap + (long)n * g.ih * g.iw;
+                for (int i = 0; i < g.kh; i++) {
+                    const int y = oh - g.ph + i;
+                    if (y < 0 || y >= g.ih) continue;
+                    for (int j = 0; j < g.kw; j++) {
+                        const int x = ow - g.pw + j;
+                        if (x < 0 || x >= g.iw) continue;
+                        kk = __fadd_rn(kk, __fmul_rn(__ldg(img + y * g.iw + x), g.inv_khw));
+                    }
+                }
+                if (g.kmap_out && cgroup == 0 && nt == 0) g.kmap_out[pix] = kk;
+            }
+        }
         const int oc0 = nt * g.n_tile;
         const int n_valid = min(g.n_tile, g.oc - oc0);  // real filters in this tile
         ok = mbar_wait(smem_u32(&ctl->acc_full[b]), acc_phase, abort_flag, g.error, 4);
@@ -695,8 +718,8 @@ bool encode_bytes_2d(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t 
 }  // namespace
 
 cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *bin_w,
-                                const float *alpha, const float *k, float *dst, int32_t *sums,
-                                int *error_word, cudaStream_t s) {
+                                const float *alpha, const float *k, const float *a, float *k_out,
+                                float *dst, int32_t *sums, int *error_word, cudaStream_t s) {
     if (p.q_total == 0) return cudaSuccess;
     CUtensorMap map_a, map_b;
     if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk, BM) ||
@@ -705,7 +728,9 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
         return cudaErrorNotSupported;
 
     TcArgs g;
-    g.alpha = alpha; g.kmap = k; g.dst = dst; g.sums = sums; g.error = error_word;
+    g.alpha = alpha; g.kmap = k; g.amap = a; g.kmap_out = k_out; g.dst = dst; g.sums = sums;
+    g.error = error_word;
+    g.inv_khw = p.inv_khw; g.ih = p.ih; g.iw = p.iw; g.kh = p.kh;
     g.q_total = p.q_total;
     g.m_tiles = (int)((p.q_total + BM - 1) / BM);
     g.n_tiles = p.ocp16 / p.n_tile;

@@ -42,9 +42,11 @@ cudaError_t launch_conv_popc(const Plan &p, const uint32_t *bin_src, const uint3
 
 // The same contract on the tensor cores (tcgen05.mma kind::i8 over +-1 bytes, plan.hpp's framed
 // layout). `error_word` is a device int the kernel sets non-zero if one of its bounded waits
-// ran out; it is never cleared by the kernel.
+// ran out; it is never cleared by the kernel. With k == nullptr the epilogue box-filters K from
+// the mean-|x| map `a` itself (same arithmetic as launch_box_filter) and records it in k_out,
+// which saves the separate stencil launch in the fused forward call.
 cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *bin_w,
-                                const float *alpha, const float *k, float *dst, int32_t *sums,
-                                int *error_word, cudaStream_t s);
+                                const float *alpha, const float *k, const float *a, float *k_out,
+                                float *dst, int32_t *sums, int *error_word, cudaStream_t s);
 
 }  // namespace xb200
