@@ -59,6 +59,25 @@ def conv_out(L):
     return ((L.ih + 2 * L.pw - L.kh) // L.sh + 1, (L.iw + 2 * L.pw - L.kw) // L.sw + 1)
 
 
+def pipe_probe():
+    """Live ceilings of the candidate instruction paths (xnor_nn_b200/pipe_probe, built with the
+    library): binary TOPS of the LOP3+POPC tile, of mma.sync b1 and of tcgen05.mma kind::i8."""
+    exe = os.path.join(ROOT, "xnor_nn_b200", "pipe_probe")
+    if not os.path.exists(exe):
+        return None
+    try:
+        out = subprocess.run([exe], capture_output=True, text=True, timeout=120).stdout
+        return json.loads(out.strip().splitlines()[-1])
+    except (OSError, ValueError, IndexError, subprocess.TimeoutExpired):
+        return None
+
+
+# DRAM bytes of one convolution launch on the benchmark layer, from the ncu capture summarised
+# in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum): the packed operands are read once,
+# the 44 MB result is still in L2 when the kernel ends.
+NCU_CONV_TRAFFIC = {("B", "tcgen05_i8"): 20.37e6 + 0.31e6}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -307,19 +326,27 @@ def run_ours(args, L, rank, world, local_rank):
     conv_ms = timed(conv_only, n_k)
     bin_ms = timed(bin_only, n_k)
     pk, pk_kind = peaks()
+    probe = pipe_probe() if rank == 0 else None
     conv_tops = binary_ops(L, mb) / (conv_ms * 1e-3) / 1e12
+    probe_peak = None
     if kernel_name == "tcgen05_i8":
         # 8-bit operands issue at twice the 16-bit rate on the same tensor pipe
         peak = 2.0 * pk["bf16_tflops"]
         peak_note = "2 x %s bf16 dense burst (8-bit operands)" % pk_kind
         bound = "tensor"
+        probe_peak = probe.get("tcgen05_i8_tops") if probe else None
     else:
-        peak = None
-        peak_note = "no measured peak for this pipe"
+        key = "mma_b1_binary_tops" if kernel_name == "mma_b1" else "popc_binary_tops"
+        peak = probe.get(key) if probe else None
+        peak_note = "pipe_probe, measured in this run (no MEASURED_PEAKS entry for this pipe)"
         bound = "tensor" if kernel_name == "mma_b1" else "int_pipe"
+        probe_peak = peak
     roofline = {"kernel": "conv_" + kernel_name, "bound": bound, "achieved": conv_tops,
                 "peak": peak, "unit": "TFLOP/s", "frac": (conv_tops / peak) if peak else None,
-                "traffic": None, "peak_source": peak_note, "ms": conv_ms,
+                "traffic": NCU_CONV_TRAFFIC.get((args.config, kernel_name)) if world == 1 else None,
+                "peak_source": peak_note, "ms": conv_ms,
+                "frac_of_probe_peak": (conv_tops / probe_peak) if probe_peak else None,
+                "pipe_probe": probe,
                 "binarize": {"bound": "hbm", "achieved": 4.0 * n_src / (bin_ms * 1e-3) / 1e9,
                              "peak": pk["hbm_gbs"], "unit": "GB/s",
                              "frac": 4.0 * n_src / (bin_ms * 1e-3) / 1e9 / pk["hbm_gbs"],

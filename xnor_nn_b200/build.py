@@ -17,6 +17,8 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libxnor_nn.so")
+PROBE_SRC = os.path.join(CSRC, "probe", "pipe_probe.cu")
+PROBE = os.path.join(PKG, "pipe_probe")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -61,6 +63,10 @@ def build(force=False, verbose=False):
         cmd = [NVCC] + ARCH + ["-shared", "-cudart", "static", "-ccbin", "/usr/bin/g++",
                                "-o", LIB] + objs
         subprocess.check_call(cmd)
+    # The pipe-rate probe is a stand-alone program (measured ceilings for the benchmark).
+    if force or _stale(PROBE, [PROBE_SRC, os.path.abspath(__file__)]):
+        subprocess.check_call([NVCC] + ARCH + ["-O3", "-std=c++17", "-lineinfo", "-ccbin",
+                                               "/usr/bin/g++", "-o", PROBE, PROBE_SRC])
     return LIB
 
 

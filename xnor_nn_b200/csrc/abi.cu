@@ -63,6 +63,10 @@ struct ResCtx {
     int32_t *sums_stage = nullptr;
     size_t sums_bytes = 0;
     int *error_word = nullptr;  // device int: set by a kernel whose bounded wait ran out
+    // host-pointer pipeline: copy engines on their own streams, events to chain the slices
+    static constexpr int kMaxSlices = 8;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_in[kMaxSlices] = {}, ev_done[kMaxSlices] = {}, ev_edge = nullptr;
 };
 
 std::mutex g_mu;
@@ -386,6 +390,13 @@ void xnor_nn_free_resources(xnor_nn_resources_t res) {
             if (x->stage[i]) cudaFree(x->stage[i]);
         if (x->sums_stage) cudaFree(x->sums_stage);
         if (x->error_word) cudaFree(x->error_word);
+        if (x->copy_in) cudaStreamDestroy(x->copy_in);
+        if (x->copy_out) cudaStreamDestroy(x->copy_out);
+        for (int i = 0; i < ResCtx::kMaxSlices; i++) {
+            if (x->ev_in[i]) cudaEventDestroy(x->ev_in[i]);
+            if (x->ev_done[i]) cudaEventDestroy(x->ev_done[i]);
+        }
+        if (x->ev_edge) cudaEventDestroy(x->ev_edge);
         if (x->own_stream) cudaStreamDestroy(x->own_stream);
         (void)cudaGetLastError();
         delete x;
@@ -444,6 +455,105 @@ void xnor_nn_binarize_weights_float(const xnor_nn_convolution_t *c, const float 
 
 // ---- extensions --------------------------------------------------------------------------------
 
+}  // extern "C"
+#pragma GCC visibility pop
+
+namespace {
+
+// A contiguous run of images of a plan: the same layer with a smaller minibatch, and the byte
+// offset at which its data starts in every buffer. Every kernel is independent per image
+// (upstream's outermost loop is the minibatch everywhere, e.g.
+// src/default/bcast_convolution_default.cpp:61), so a slice is a complete problem of its own.
+struct Slice {
+    Plan p;
+    size_t src, bin_src, a, k, dst;
+};
+
+Slice slice_of(const Plan &p, int first, int count) {
+    Slice s;
+    s.p = p;
+    s.p.mb = count;
+    s.p.q_total = (long)count * p.hp * p.wp;
+    s.p.rows = p.lead + s.p.q_total + 256 + (long)p.kh * p.wp + p.kw;
+    s.src = (size_t)first * p.ic * p.ih * p.iw * sizeof(float);
+    s.a = (size_t)first * p.ih * p.iw * sizeof(float);
+    s.k = (size_t)first * p.oh * p.ow * sizeof(float);
+    s.dst = (size_t)first * p.oc * p.oh * p.ow * sizeof(float);
+    s.bin_src = p.family == kPopc      ? (size_t)first * p.ih * p.iw * p.icw * sizeof(uint32_t)
+                : p.family == kTcgen05 ? (size_t)first * p.hp * p.wp * p.icp
+                                       : (size_t)first * p.hp * p.wp * p.icw * sizeof(uint32_t);
+    return s;
+}
+
+// binarize + A, K, convolution of one slice, device pointers, on the context's stream.
+xnor_nn_status_t enqueue_forward(const Slice &sl, ResCtx *x, xnor_nn_resources_t res,
+                                 const float *src, float *dst) {
+    xnor_nn_resources_t sub;
+    for (int i = 0; i < xnor_nn_resource_number; i++) sub[i] = res[i];
+    sub[xnor_nn_resource_bin_src] = (char *)res[xnor_nn_resource_bin_src] + sl.bin_src;
+    sub[xnor_nn_resource_a] = (char *)res[xnor_nn_resource_a] + sl.a;
+    sub[xnor_nn_resource_k] = (char *)res[xnor_nn_resource_k] + sl.k;
+    CU(launch_binarize_data(sl.p, src, sub[xnor_nn_resource_bin_src],
+                            (float *)sub[xnor_nn_resource_a], x->stream));
+    const bool fuse_k = sl.p.family == kTcgen05;
+    if (!fuse_k)
+        CU(launch_box_filter(sl.p, (const float *)sub[xnor_nn_resource_a],
+                             (float *)sub[xnor_nn_resource_k], x->stream));
+    return run_conv(sl.p, x, sub, dst, nullptr, fuse_k);
+}
+
+// Host source and host result: the minibatch is cut into slices whose upload, kernels and
+// download overlap (PCIe is full duplex and both copy engines run beside the SMs), so the call
+// costs about the longer of the two transfers instead of their sum plus the kernels.
+xnor_nn_status_t forward_host_pipelined(const Plan &p, ResCtx *x, xnor_nn_resources_t res) {
+    const char *h_src = (const char *)res[xnor_nn_resource_user_src];
+    char *h_dst = (char *)res[xnor_nn_resource_user_dst];
+    xnor_nn_status_t st = ensure_stage(x, 0, src_bytes(p));
+    if (st == xnor_nn_success) st = ensure_stage(x, 2, dst_elems(p) * sizeof(float));
+    if (st != xnor_nn_success) return st;
+    if (!x->copy_in) {
+        CU(cudaStreamCreateWithFlags(&x->copy_in, cudaStreamNonBlocking));
+        CU(cudaStreamCreateWithFlags(&x->copy_out, cudaStreamNonBlocking));
+        for (int i = 0; i < ResCtx::kMaxSlices; i++) {
+            CU(cudaEventCreateWithFlags(&x->ev_in[i], cudaEventDisableTiming));
+            CU(cudaEventCreateWithFlags(&x->ev_done[i], cudaEventDisableTiming));
+        }
+        CU(cudaEventCreateWithFlags(&x->ev_edge, cudaEventDisableTiming));
+    }
+    int slices = p.mb / 8;
+    if (slices > ResCtx::kMaxSlices) slices = ResCtx::kMaxSlices;
+    if (slices < 1) slices = 1;
+    // the copy streams start after whatever the caller already queued on the main stream
+    CU(cudaEventRecord(x->ev_edge, x->stream));
+    CU(cudaStreamWaitEvent(x->copy_in, x->ev_edge, 0));
+    CU(cudaStreamWaitEvent(x->copy_out, x->ev_edge, 0));
+    for (int i = 0; i < slices; i++) {
+        const int first = (int)((long)p.mb * i / slices);
+        const int count = (int)((long)p.mb * (i + 1) / slices) - first;
+        const Slice sl = slice_of(p, first, count);
+        char *d_src = (char *)x->stage[0] + sl.src;
+        char *d_dst = (char *)x->stage[2] + sl.dst;
+        CU(cudaMemcpyAsync(d_src, h_src + sl.src, src_bytes(sl.p), cudaMemcpyHostToDevice,
+                           x->copy_in));
+        CU(cudaEventRecord(x->ev_in[i], x->copy_in));
+        CU(cudaStreamWaitEvent(x->stream, x->ev_in[i], 0));
+        st = enqueue_forward(sl, x, res, (const float *)d_src, (float *)d_dst);
+        if (st != xnor_nn_success) return st;
+        CU(cudaEventRecord(x->ev_done[i], x->stream));
+        CU(cudaStreamWaitEvent(x->copy_out, x->ev_done[i], 0));
+        CU(cudaMemcpyAsync(h_dst + sl.dst, d_dst, dst_elems(sl.p) * sizeof(float),
+                           cudaMemcpyDeviceToHost, x->copy_out));
+    }
+    CU(cudaEventRecord(x->ev_edge, x->copy_out));
+    CU(cudaStreamWaitEvent(x->stream, x->ev_edge, 0));
+    return sync_and_check(x);
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
 xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_resources_t res) {
     if (!c || !res || !res[xnor_nn_resource_user_src] || !res[xnor_nn_resource_user_dst] ||
         !res[xnor_nn_resource_bin_src] || !res[xnor_nn_resource_bin_weights] ||
@@ -456,6 +566,9 @@ xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_re
     if (!p->formats_ok) return xnor_nn_unimplemented;
     DeviceGuard dg(x->device);
     log_exec(*p, "fused forward");
+    if (p->mb >= 16 && !on_device(res[xnor_nn_resource_user_src]) &&
+        !on_device(res[xnor_nn_resource_user_dst]))
+        return forward_host_pipelined(*p, x, res);
     const void *src = nullptr;
     bool staged = false;
     xnor_nn_status_t st = stage_in(x, 0, res[xnor_nn_resource_user_src], src_bytes(*p), &src, &staged);
@@ -468,13 +581,7 @@ xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_re
         if (st != xnor_nn_success) return st;
         dst = (float *)x->stage[2];
     }
-    CU(launch_binarize_data(*p, (const float *)src, res[xnor_nn_resource_bin_src],
-                            (float *)res[xnor_nn_resource_a], x->stream));
-    const bool fuse_k = p->family == kTcgen05;
-    if (!fuse_k)
-        CU(launch_box_filter(*p, (const float *)res[xnor_nn_resource_a],
-                             (float *)res[xnor_nn_resource_k], x->stream));
-    st = run_conv(*p, x, res, dst, nullptr, fuse_k);
+    st = enqueue_forward(slice_of(*p, 0, p->mb), x, res, (const float *)src, dst);
     if (st != xnor_nn_success) return st;
     if (!direct)
         CU(cudaMemcpyAsync(user, dst, dst_elems(*p) * sizeof(float), cudaMemcpyDeviceToHost,
