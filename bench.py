@@ -48,6 +48,7 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0,
                     help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-probe", action="store_true", help="skip the pipe-rate probe")
     return ap.parse_args()
 
 
@@ -252,9 +253,9 @@ def run_ours(args, L, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    assert L.mb % world == 0, "minibatch must split evenly"
-    mb = L.mb // world
-    first = rank * mb
+    from xnor_nn_b200.sharding import shard_range
+    first, last = shard_range(L.mb, rank, world)
+    mb = last - first
     oh, ow = conv_out(L)
     kernel = {"auto": xb.KERNEL_AUTO, "popc": xb.KERNEL_POPC, "mma_b1": xb.KERNEL_MMA_B1,
               "tcgen05_i8": xb.KERNEL_TCGEN05_I8}[args.kernel]
@@ -326,7 +327,7 @@ def run_ours(args, L, rank, world, local_rank):
     conv_ms = timed(conv_only, n_k)
     bin_ms = timed(bin_only, n_k)
     pk, pk_kind = peaks()
-    probe = pipe_probe() if rank == 0 else None
+    probe = pipe_probe() if rank == 0 and not args.no_probe else None
     conv_tops = binary_ops(L, mb) / (conv_ms * 1e-3) / 1e12
     probe_peak = None
     if kernel_name == "tcgen05_i8":

@@ -161,7 +161,7 @@ int main() {
     cudaMemset(buf, 0x5a, 1 << 24);
     cudaMalloc(&err, 4);
     cudaMemset(err, 0, 4);
-    const int blocks = sms * 8, threads = 256, iters = 20000;
+    const int blocks = sms * 8, threads = 256, iters = 2000;
     const double nthreads = (double)blocks * threads;
 
     float ms = best_ms([&] { popc_tile<<<blocks, threads>>>(buf, buf + 4096, iters / 4); });
