@@ -79,6 +79,24 @@ xnor_nn_status_t xnor_nn_b200_synchronize(xnor_nn_resources_t res);
  * reports through the status code alone (src/status.cpp:3-15). */
 const char *xnor_nn_b200_last_error(void);
 
+/* K = box filter of mean|x| (what the calculate_k executor computes into res[k]) for callers
+ * that cannot allocate device memory when they need it: code that runs while a stream is being
+ * captured into a CUDA graph, servers whose arena owns all device memory, sandboxed plugins.
+ * It has no counterpart in the reference and needs no xnor_nn_allocate_resources: the mean-|x|
+ * scratch is a fixed array inside the library (xnor_nn_b200_noalloc_max_pixels() floats, 4 MiB,
+ * held by every GPU that loads the library). `src_device` (the layer's source tensor, in the
+ * descriptor's src_format) and `k_device` (mb*oh*ow floats) are device memory the caller already
+ * owns; the work is enqueued on `cuda_stream` (a cudaStream_t, NULL = default stream).
+ * Limits: mb*ih*iw above the maximum is refused with xnor_nn_error_invalid_input; all calls on a
+ * device share the one array, so calls that overlap on the GPU race and must be serialised by the
+ * caller; the first call on a device resolves the array's address and should be made before any
+ * stream capture starts. Calls no cudaMalloc/cudaFree. */
+xnor_nn_status_t xnor_nn_b200_calculate_k_noalloc(const xnor_nn_convolution_t *c,
+                                                  const float *src_device, float *k_device,
+                                                  void *cuda_stream);
+long xnor_nn_b200_noalloc_max_pixels(void);
+const char *xnor_nn_b200_noalloc_last_error(void);
+
 /* Number of kernels this library has launched in this process, for benchmark accounting. */
 long xnor_nn_b200_kernel_launches(void);
 

@@ -84,6 +84,9 @@ def lib():
         L.xnor_nn_b200_synchronize.argtypes = [rp]
         L.xnor_nn_b200_last_error.restype = C.c_char_p
         L.xnor_nn_b200_kernel_launches.restype = C.c_long
+        L.xnor_nn_b200_calculate_k_noalloc.argtypes = [dp, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.xnor_nn_b200_noalloc_max_pixels.restype = C.c_long
+        L.xnor_nn_b200_noalloc_last_error.restype = C.c_char_p
         _lib = L
     return _lib
 
