@@ -158,6 +158,7 @@ def upstream_forward_seconds(L, mb, budget_s, steps=None, warmup=1):
     import ctypes as C
     from oracle.pyoracle import UpstreamRef, UpstreamConv
     ref = UpstreamRef()
+    host_threads()
     cfg_name = [k for k, v in synth.CONFIGS.items() if v.name == L.name][0]
     src, w = synth.make_inputs(cfg_name, mb=mb)
     c = UpstreamConv()
@@ -188,9 +189,15 @@ def upstream_forward_seconds(L, mb, budget_s, steps=None, warmup=1):
 
 
 def host_threads():
+    """OpenMP threads the upstream library will use: all cores this process may run on. (A
+    launcher such as torchrun exports OMP_NUM_THREADS=1 for its workers; the CPU arm is meant to
+    use the whole host, so the team size is set explicitly.)"""
     try:
         import ctypes
-        return ctypes.CDLL("libgomp.so.1").omp_get_max_threads()
+        omp = ctypes.CDLL("libgomp.so.1")
+        want = len(os.sched_getaffinity(0))
+        omp.omp_set_num_threads(want)
+        return omp.omp_get_max_threads()
     except OSError:
         return os.cpu_count()
 

@@ -12,7 +12,7 @@
 // Positions on the frame border are computed and dropped by the epilogue.
 //
 // One CTA per SM, persistent over (position tile, filter tile) pairs:
-//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, no multicast) into rings of
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, each CTA fetching its own tiles) into rings of
 //               shared-memory buffers; completion is counted on an mbarrier per buffer
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma.kind::i8 (M=128, N<=256,
 //               K=32 per instruction) into one of two accumulators in tensor memory, and
