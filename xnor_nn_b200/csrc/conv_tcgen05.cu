@@ -68,7 +68,6 @@ struct TcArgs {
     uint32_t desc_hi;  // upper 32 bits of the shared-memory matrix descriptors
     uint32_t a_bytes, stage_bytes, tx_bytes;
     int dst_nhwc;
-    int debug;
     // slab kernel only
     int group;            // channel chunks per weight stage (G)
     int groups_per_tile;  // chunks_per_tap / G
@@ -267,7 +266,7 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
-        if (!g.sums && !g.dst_nhwc && !(g.debug & 2)) {
+        if (!g.sums && !g.dst_nhwc) {
             // NCHW floats: for one filter the 32 lanes hold 32 neighbouring pixels, so a
             // store instruction writes one contiguous run.
             float *out = g.dst + ((long)n * g.oc + oc0) * ohw + r;
@@ -282,11 +281,26 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
                 tc_wait_ld();
                 if (valid) {
                     const int lim = n_valid - c0;
+                    float *o = out + (long)c0 * ohw;
+                    if (alpha_in_smem && lim >= 32) {
+                        // full group: alpha by 16-byte shared loads, one running pointer
+                        const float4 *a4 = reinterpret_cast<const float4 *>(al + c0);
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (j < lim)
-                            out[(long)(c0 + j) * ohw] =
-                                __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk);
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 a = a4[j >> 2];
+                            o[0] = __fmul_rn(__fmul_rn((float)(int)v[j], a.x), kk);
+                            o[ohw] = __fmul_rn(__fmul_rn((float)(int)v[j + 1], a.y), kk);
+                            o[2 * ohw] = __fmul_rn(__fmul_rn((float)(int)v[j + 2], a.z), kk);
+                            o[3 * ohw] = __fmul_rn(__fmul_rn((float)(int)v[j + 3], a.w), kk);
+                            o += 4 * ohw;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < lim)
+                                o[(long)j * ohw] =
+                                    __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk);
+                    }
                 }
             }
         } else {
@@ -294,7 +308,7 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
                 uint32_t v[16];
                 tc_ld16(taddr + (uint32_t)c0, v);
                 tc_wait_ld();
-                if (valid && !(g.debug & 2)) {
+                if (valid) {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int oc = oc0 + c0 + j;
@@ -384,15 +398,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     armed &= ~(1u << stage);
                     const uint32_t bar = smem_u32(&ctl->full[stage]);
                     const uint32_t sa = stage0 + (uint32_t)stage * g.stage_bytes;
-                    if (g.debug & 1) {
-                        mbar_arrive(bar);
-                    } else {
-                        mbar_expect_tx(bar, g.tx_bytes);
-                        tma_load_2d(sa, &map_a, chunk * g.kchunk, row, bar);
-                        tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
-                        armed |= 1u << stage;
-                        armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-                    }
+                    mbar_expect_tx(bar, g.tx_bytes);
+                    tma_load_2d(sa, &map_a, chunk * g.kchunk, row, bar);
+                    tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                     if (++chunk == g.chunks_per_tap) {  // next filter tap
                         chunk = 0;
@@ -739,7 +749,6 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.kw = p.kw; g.ph = p.ph; g.pw = p.pw; g.wp = p.wp; g.hp = p.hp; g.lead = p.lead;
     g.oh = p.oh; g.ow = p.ow; g.oc = p.oc; g.ocp16 = p.ocp16;
     g.dst_nhwc = p.dst_nhwc;
-    { const char *e = getenv("XNOR_NN_B200_DEBUG"); g.debug = e ? atoi(e) : 0; }
     // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N and M encoded
     g.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.n_tile >> 3) << 17) |
               ((uint32_t)(BM >> 4) << 24);
@@ -780,7 +789,9 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     // The slab kernel wins where it packs more MMAs into a weight stage than the per-tap kernel
     // can (measured: 93 vs 131 us on the 5x5 / 96-channel layer); with a single chunk per stage
     // the per-tap kernel is a little faster (39 vs 43 us on conv4).
-    const bool use_slab = slab_rows <= 256 && ring >= 3 && (group > 1 || (g.debug & 2048)) && !(g.debug & 1024);
+    // XNOR_NN_B200_TCGEN05_VARIANT=slab|pertap overrides the choice (for comparing the two).
+    const char *variant = getenv("XNOR_NN_B200_TCGEN05_VARIANT");
+    const bool use_slab = slab_rows <= 256 && ring >= 3 && (variant ? variant[0] == 's' : group > 1);
 
     cudaError_t e;
     size_t smem;

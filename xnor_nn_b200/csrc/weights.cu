@@ -60,16 +60,41 @@ __global__ void pack_weight_bytes_kernel(const WArgs g, uint32_t *out, int icp, 
     out[i] = v;
 }
 
-__global__ void alpha_kernel(const WArgs g, float *alpha, float inv_chw) {
-    const int oc = blockIdx.x * blockDim.x + threadIdx.x;
-    if (oc >= g.oc) return;
+// alpha[oc] = sum over (ic, kh, kw) ascending of |w| * (1/(IC*KH*KW)), one thread per filter so
+// that the additions happen in upstream's order. A block owns 32 filters; the weights are staged
+// through shared memory in chunks so that the global reads are coalesced (OIHW: each filter's
+// weights are one contiguous run; HWIO: 32 neighbouring filters are contiguous for each (tap, ic)).
+constexpr int ACH = 128;  // elements of the (ic, kh, kw) walk per chunk
+
+__global__ void __launch_bounds__(256) alpha_kernel(const WArgs g, float *alpha, float inv_chw) {
+    __shared__ float t[32][ACH + 1];
+    const int oc0 = blockIdx.x * 32;
+    const int n = g.ic * g.kh * g.kw, khw = g.kh * g.kw;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float acc = 0.f;
-    for (int c = 0; c < g.ic; c++)
-        for (int kh = 0; kh < g.kh; kh++)
-            for (int kw = 0; kw < g.kw; kw++)
-                acc = __fadd_rn(acc, __fmul_rn(fabsf(__ldg(g.w + w_index(g, oc, c, kh, kw))),
-                                               inv_chw));
-    alpha[oc] = acc;
+    for (int e0 = 0; e0 < n; e0 += ACH) {
+        const int ne = min(ACH, n - e0);
+        if (!g.hwio) {
+            // warp w stages filters w, w+8, ...: lanes walk the contiguous run of one filter
+            for (int f = warp; f < 32; f += 8)
+                for (int e = lane; e < ne; e += 32)
+                    t[f][e] = oc0 + f < g.oc ? fabsf(__ldg(g.w + (long)(oc0 + f) * n + e0 + e)) : 0.f;
+        } else {
+            // lanes walk 32 neighbouring filters of one (ic, kh, kw) element
+            for (int e = warp; e < ne; e += 8) {
+                const int idx = e0 + e;  // position in upstream's (ic, kh, kw) walk
+                const int c = idx / khw, tap = idx - c * khw;
+                t[lane][e] = oc0 + lane < g.oc
+                                 ? fabsf(__ldg(g.w + ((long)tap * g.ic + c) * g.oc + oc0 + lane))
+                                 : 0.f;
+            }
+        }
+        __syncthreads();
+        if (warp == 0)
+            for (int e = 0; e < ne; e++) acc = __fadd_rn(acc, __fmul_rn(t[lane][e], inv_chw));
+        __syncthreads();
+    }
+    if (warp == 0 && oc0 + lane < g.oc) alpha[oc0 + lane] = acc;
 }
 
 __global__ void op_count_kernel(int32_t *op_c, int ic, int ih, int iw, int oh, int ow, int kh,
@@ -108,7 +133,7 @@ cudaError_t launch_binarize_weights(const Plan &p, const float *w, void *bin_w, 
     note_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    alpha_kernel<<<(p.oc + 31) / 32, 32, 0, s>>>(g, alpha, p.inv_chw);
+    alpha_kernel<<<(p.oc + 31) / 32, 256, 0, s>>>(g, alpha, p.inv_chw);
     note_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
