@@ -192,6 +192,9 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
         __syncthreads();
     }
     if (WITH_A && warp == 0 && live) g.a[px] = acc;
+    // Released only now: a dependent grid that started earlier would take SMs away from blocks
+    // of this grid that have not been scheduled yet.
+    dependency_release();
 }
 
 struct BoxArgs {

@@ -363,6 +363,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // Everything above touched only this CTA's own shared and tensor memory; from here on the
+    // kernel reads what earlier kernels of the stream produced.
+    dependency_wait();
     const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
     if (alpha_in_smem)
         for (int i = threadIdx.x; i < g.ocp16; i += kThreads)
@@ -476,6 +479,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
+    dependency_release();  // the next kernel may set up while this CTA winds down
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -528,6 +532,9 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // Everything above touched only this CTA's own shared and tensor memory; from here on the
+    // kernel reads what earlier kernels of the stream produced.
+    dependency_wait();
     const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
     if (alpha_in_smem)
         for (int i = threadIdx.x; i < g.ocp16; i += kThreads)
@@ -679,6 +686,7 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
         epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
+    dependency_release();  // the next kernel may set up while this CTA winds down
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -819,9 +827,8 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles = g.m_tiles * g.n_tiles;
     const int grid = tiles < sms ? tiles : sms;
-    kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, g);
     note_launch();
-    return cudaGetLastError();
+    return launch_overlapped(kernel, dim3(grid), dim3(kThreads), smem, s, map_a, map_b, g);
 }
 
 }  // namespace xb200

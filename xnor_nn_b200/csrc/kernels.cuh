@@ -14,6 +14,40 @@ namespace xb200 {
 extern std::atomic<long> g_kernel_launches;
 inline void note_launch(int n = 1) { g_kernel_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// Launch with programmatic stream serialisation: the grid may be scheduled while the previous
+// kernel of the stream is still draining, so that its set-up (and the launch latency itself)
+// runs under the predecessor's tail. Kernels launched this way call dependency_wait() before
+// they touch anything an earlier kernel may have written or may still be reading. Only the
+// tensor-core convolution is launched like this (measured: 2-3 us per forward pass); launching
+// the binarizer the same way made alternating binarize/convolution sequences slower.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#ifdef __CUDACC__
+// Lets the next kernel of the stream start its set-up now ...
+__device__ __forceinline__ void dependency_release() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// ... and blocks until every earlier kernel of the stream has completed and its writes are
+// visible. A no-op for grids launched the ordinary way.
+__device__ __forceinline__ void dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+
 // ---- activations -----------------------------------------------------------------------------
 // One pass over the fp32 source: sign bits into the family's packed layout and, when `a` is not
 // null, the per-pixel mean |x| map. Replaces upstream src/bcast_binarize_data.cpp:43-73 and the
