@@ -90,7 +90,7 @@ def peaks():
 # ---- clocks ------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """nvidia-smi sampled every 100 ms in the background; read-only."""
+    """nvidia-smi sampled every 25 ms in the background; read-only."""
     FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -101,7 +101,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "25"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()

@@ -96,6 +96,63 @@ def test_device_pointers_skip_staging(oracle, kernel):
     conv.close()
 
 
+def test_host_pipeline_with_uneven_slices(oracle):
+    """Host buffers of 16 or more images go through the sliced upload/compute/download
+    pipeline; 17 images split into two unequal slices."""
+    L = synth.layer_shape("A", mb=17)._replace(oc=32)
+    src, w = synth.make_inputs("A", mb=17)
+    w = np.ascontiguousarray(w[:32])
+    from oracle.pyoracle import Shape
+    want = oracle.convolution(
+        Shape.make(L.mb, L.oc, L.ic, L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw), src, w)
+    for kernel in (xb.KERNEL_TCGEN05_I8, xb.KERNEL_POPC):
+        conv = xb.Convolution(xb.ALGORITHM_BCAST, xb.NCHW, xb.OIHW, xb.NCHW, L.mb, L.oc, L.ic,
+                              L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, w, kernel=kernel)
+        dst = np.full(want["dst"].size, np.nan, np.float32)
+        conv.forward(src, dst)
+        assert np.array_equal(dst, want["dst"])
+        assert np.array_equal(conv.read(xb.SLOT_K, np.float32), want["k"])
+        conv.close()
+
+
+def test_two_threads_share_one_descriptor(oracle):
+    """One descriptor, one resource array per thread (each owns a stream and its staging
+    buffers), as upstream allows: its executors only read the descriptor."""
+    import threading
+    case = [c for c in cases.ALL_CASES if c[0] == "alexnet_conv2"][0]
+    src, w = cases.make_inputs(case)
+    want = oracle.convolution(cases.oracle_shape(case), src, w)["dst"]
+    first = _conv(case, None, w)
+    results, errors = {}, []
+
+    def work(tag):
+        try:
+            res = (C.c_void_p * xb.N_SLOTS)()
+            L = xb.lib()
+            assert L.xnor_nn_allocate_resources(C.byref(first.c), res) == xb.SUCCESS
+            res[xb.SLOT_USER_WEIGHTS] = w.ctypes.data
+            assert first.c.binarize_weights(C.addressof(first.c), res) == xb.SUCCESS
+            out = np.empty(want.size, np.float32)
+            for _ in range(5):
+                res[xb.SLOT_USER_SRC] = src.ctypes.data
+                res[xb.SLOT_USER_DST] = out.ctypes.data
+                assert L.xnor_nn_b200_forward(C.byref(first.c), res) == xb.SUCCESS
+            L.xnor_nn_free_resources(res)
+            results[tag] = out
+        except Exception as e:  # surfaced in the main thread
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(3)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for out in results.values():
+        assert np.array_equal(out, want)
+    first.close()
+
+
 def test_change_weights(oracle):
     case = [c for c in cases.ALL_CASES if c[0] == "mnist_24to48"][0]
     src, w = cases.make_inputs(case)
