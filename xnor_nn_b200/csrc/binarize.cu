@@ -110,8 +110,8 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 // ---- NCHW source, +-1 bytes on the frame: the layout the tensor-core convolution reads -------
 //
 // A block of four warps owns 32 neighbouring pixels and walks the channels in chunks of 128.
-// All warps load (lane = pixel, so a load instruction reads one 128-byte line of a channel
-// plane; 32 independent loads per thread, issued one chunk ahead so that they are in flight
+// All warps load (lane = pixel, warp w the w-th quarter of the chunk's channels, so a load
+// instruction reads one 128-byte line of a channel plane; 32 independent loads per thread, issued one chunk ahead so that they are in flight
 // while the previous chunk is consumed). |x|/IC goes to a float tile and the sign byte to a byte
 // tile in shared memory. Warp 0 then adds the float tile up channel by channel, one lane per
 // pixel, which keeps upstream's summation order, while the other warps copy the byte tile out
@@ -139,26 +139,53 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
 
     const int c_end = WITH_PACK ? g.words * 4 : g.ic;  // channel extent walked
     float acc = 0.f;
+    // Warp w owns the 32 consecutive channels [32w, 32w+32) of every chunk, so four of its sign
+    // bytes make one 32-bit word of the packed row.
+    const float *pw = p + (long)(TPER * warp) * g.hw;
+    const int cw = TPER * warp;  // first channel of this warp inside a chunk
     float v[TPER];
+    if (live && TCC <= g.ic) {
 #pragma unroll
-    for (int i = 0; i < TPER; i++) {
-        const int c = warp + TWARPS * i;
-        v[i] = (live && c < g.ic) ? __ldg(p + (long)c * g.hw) : 0.f;
+        for (int i = 0; i < TPER; i++) v[i] = __ldg(pw + (long)i * g.hw);
+    } else {
+#pragma unroll
+        for (int i = 0; i < TPER; i++)
+            v[i] = (live && cw + i < g.ic) ? __ldg(pw + (long)i * g.hw) : 0.f;
     }
     for (int c0 = 0; c0 < c_end; c0 += TCC) {
+        const bool full = c0 + TCC <= g.ic;  // no channel tail in this chunk
+        if (WITH_A) {
 #pragma unroll
-        for (int i = 0; i < TPER; i++) {
-            const int cl = warp + TWARPS * i;
-            if (WITH_A) f_s[cl * TPX + lane] = __fmul_rn(fabsf(v[i]), g.inv_ic);
-            if (WITH_PACK)
-                b_s[lane * TLD + cl] = (c0 + cl < g.ic) ? (sign_clear(v[i]) ? 0x01 : 0xFF) : 0x00;
+            for (int i = 0; i < TPER; i++)
+                f_s[(cw + i) * TPX + lane] = __fmul_rn(fabsf(v[i]), g.inv_ic);
+        }
+        if (WITH_PACK) {
+            uint32_t *brow = reinterpret_cast<uint32_t *>(b_s + lane * TLD) + cw / 4;
+#pragma unroll
+            for (int j = 0; j < TPER / 4; j++) {
+                // sign bit set -> 0xFF (-1), clear -> 0x01 (+1): 0x01 ^ (sign * 0xFE) per byte
+                const uint32_t m = (__float_as_uint(v[4 * j]) >> 31) |
+                                   ((__float_as_uint(v[4 * j + 1]) >> 31) << 8) |
+                                   ((__float_as_uint(v[4 * j + 2]) >> 31) << 16) |
+                                   ((__float_as_uint(v[4 * j + 3]) >> 31) << 24);
+                uint32_t word = 0x01010101u ^ (m * 0xFEu);
+                if (!full) {  // channels past the last one are zero bytes
+                    const int left = g.ic - (c0 + cw + 4 * j);
+                    word = left >= 4 ? word : left <= 0 ? 0u : (word & (0xFFFFFFFFu >> (8 * (4 - left))));
+                }
+                brow[j] = word;
+            }
         }
         __syncthreads();
         if (c0 + TCC < c_end) {  // next chunk's loads fly while this one is consumed
+            const float *pn = pw + (long)(c0 + TCC) * g.hw;
+            if (live && c0 + 2 * TCC <= g.ic) {
 #pragma unroll
-            for (int i = 0; i < TPER; i++) {
-                const int c = c0 + TCC + warp + TWARPS * i;
-                v[i] = (live && c < g.ic) ? __ldg(p + (long)c * g.hw) : 0.f;
+                for (int i = 0; i < TPER; i++) v[i] = __ldg(pn + (long)i * g.hw);
+            } else {
+#pragma unroll
+                for (int i = 0; i < TPER; i++)
+                    v[i] = (live && c0 + TCC + cw + i < g.ic) ? __ldg(pn + (long)i * g.hw) : 0.f;
             }
         }
         if (WITH_A && warp == 0) {
