@@ -92,9 +92,18 @@ void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
         p->bytes[xnor_nn_resource_bin_weights] =
             (size_t)p->kh * p->kw * p->icw * p->ocp * sizeof(uint32_t);
     } else {
-        p->kchunk = p->ic > 64 && (div_up_i(p->ic, 32) * 32) % 128 == 0 ? 128
-                    : (div_up_i(p->ic, 32) * 32) % 64 == 0             ? 64
-                                                                        : 32;
+        // K chunk = bytes of one channel group per pipeline stage = the swizzle span. Wide
+        // chunks mean few, fat stages (4 MMAs per barrier round trip at 128 B), which is worth
+        // some zero padding of the channels: 96 channels padded to 128 run the 5x5 AlexNet layer
+        // in 67 us, as three 32-byte chunks in 89 us. Take the widest chunk that pads the
+        // channels by no more than 35 %.
+        p->kchunk = 32;
+        for (int k = 128; k >= 64; k /= 2)
+            if (div_up_i(p->ic, k) * k <= p->ic * 1.35) { p->kchunk = k; break; }
+        if (const char *e = getenv("XNOR_NN_B200_KCHUNK")) {  // tuning override: 32, 64 or 128
+            const int v = atoi(e);
+            if (v == 32 || v == 64 || v == 128) p->kchunk = v;
+        }
         p->icp = div_up_i(p->ic, p->kchunk) * p->kchunk;
         p->ocp16 = div_up_i(p->oc, 16) * 16;
         // Filter tile = UMMA N: a multiple of 16, at most 256, that splits ocp16 evenly; the
