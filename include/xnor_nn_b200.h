@@ -24,7 +24,7 @@ extern "C" {
 typedef enum {
     xnor_nn_b200_kernel_auto = -1,
     xnor_nn_b200_kernel_popc = 0,       /* LOP3+POPC integer pipe; every shape and format     */
-    xnor_nn_b200_kernel_mma_b1 = 1,     /* mma.sync m16n8k256 xor.popc; unit stride           */
+    xnor_nn_b200_kernel_mma_b1 = 1,     /* mma.sync b1: measured slower than popc, served by popc */
     xnor_nn_b200_kernel_tcgen05_i8 = 2  /* tcgen05.mma kind::i8 on +-1 bytes; unit stride     */
 } xnor_nn_b200_kernel_t;
 

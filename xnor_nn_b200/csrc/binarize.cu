@@ -11,7 +11,7 @@ namespace xb200 {
 
 namespace {
 
-enum OutKind { kBitsDense = 0, kBitsFramed = 1, kBytesFramed = 2 };
+enum OutKind { kBitsDense = 0, kBytesFramed = 2 };
 
 struct BinArgs {
     const float *src;
@@ -280,7 +280,6 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
     }
     switch (p.family) {
         case kPopc: binarize_kernel<kBitsDense, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
-        case kMmaB1: binarize_kernel<kBitsFramed, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
         default: binarize_kernel<kBytesFramed, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
     }
     note_launch();

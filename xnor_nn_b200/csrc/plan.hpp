@@ -15,7 +15,7 @@ namespace xb200 {
 // so the choice is fixed at init and every executor of the descriptor follows it.
 enum Family : int {
     kPopc = 0,     // bits, LOP3 + POPC on the integer pipe; any stride, padding and format
-    kMmaB1 = 1,    // bits, mma.sync m16n8k256 xor.popc (legacy tensor path); stride 1
+    kMmaB1 = 1,    // mma.sync m16n8k256 xor.popc: measured, ruled out, never selected
     kTcgen05 = 2,  // +-1 int8, tcgen05.mma kind::i8 into tensor memory; stride 1
     kAuto = -1,
 };
@@ -33,7 +33,7 @@ struct Plan {
     float inv_khw;  // 1.f / KH / KW                (src/bcast_calculate_k.cpp:43)
     float inv_chw;  // 1.f / (IC*KH*KW)             (src/bcast_binarize_weights.cpp:95)
 
-    // ---- bit layouts (kPopc, kMmaB1) -----------------------------------------------------
+    // ---- bit layout (kPopc) -------------------------------------------------------------
     // activations: uint32 [mb][ih][iw][icw]; channel c is bit (31 - c%32) of word c/32; bits
     //              past the last channel are 0.
     // weights:     uint32 [kh][kw][icw][ocp]; same bit order, bits past the last channel 0,
