@@ -47,6 +47,7 @@ SHAPE_CASES = [
     _c("ph0_pw1", 1, 16, 20, 9, 9, 3, 3, ph=0, pw=1),
     _c("one_by_one", 2, 40, 130, 7, 7, 1, 1),
     _c("single_pixel_out", 1, 8, 33, 3, 3, 3, 3),
+    _c("oc260_two_filter_tiles", 1, 260, 16, 6, 6, 3, 3, ph=1, pw=1),
 ]
 
 # Tensor formats other than NCHW/OIHW/NCHW
