@@ -303,6 +303,28 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
                     }
                 }
             }
+        } else if (!g.sums && g.dst_nhwc && (g.oc & 3) == 0) {
+            // NHWC floats: a thread owns one pixel and 16 neighbouring filters at a time, which
+            // are contiguous in the result: four 16-byte stores.
+            float *out = g.dst + pix * g.oc + oc0;
+            const float *al = alpha_in_smem ? ctl->alpha + oc0 : g.alpha + oc0;
+            for (int c0 = 16 * cgroup; c0 < g.n_tile; c0 += 16 * cgroups) {
+                uint32_t v[16];
+                tc_ld16(taddr + (uint32_t)c0, v);
+                tc_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        if (c0 + j >= n_valid) break;  // oc and n_valid are multiples of 4
+                        float4 x;
+                        x.x = __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk);
+                        x.y = __fmul_rn(__fmul_rn((float)(int)v[j + 1], al[c0 + j + 1]), kk);
+                        x.z = __fmul_rn(__fmul_rn((float)(int)v[j + 2], al[c0 + j + 2]), kk);
+                        x.w = __fmul_rn(__fmul_rn((float)(int)v[j + 3], al[c0 + j + 3]), kk);
+                        *reinterpret_cast<float4 *>(out + c0 + j) = x;
+                    }
+                }
+            }
         } else {
             for (int c0 = 16 * cgroup; c0 < g.n_tile; c0 += 16 * cgroups) {
                 uint32_t v[16];
