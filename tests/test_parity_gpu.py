@@ -153,6 +153,23 @@ def test_two_threads_share_one_descriptor(oracle):
     first.close()
 
 
+def test_more_filters_than_the_staged_alpha_table(oracle):
+    """2100 filters: nine filter tiles, and alpha is read from global memory instead of the
+    2048-entry shared-memory copy the tensor-core epilogue normally uses."""
+    from oracle.pyoracle import Shape
+    mb, oc, ic, ih, iw = 2, 2100, 16, 6, 6
+    src = synth.normal(101, mb * ic * ih * iw).reshape(mb, ic, ih, iw)
+    w = synth.normal(102, oc * ic * 9, 0.05).reshape(oc, ic, 3, 3)
+    want = oracle.convolution(Shape.make(mb, oc, ic, ih, iw, 3, 3, 1, 1, 1, 1), src, w)
+    conv = xb.Convolution(xb.ALGORITHM_BCAST, xb.NCHW, xb.OIHW, xb.NCHW, mb, oc, ic, ih, iw, 3, 3,
+                          1, 1, 1, 1, w, kernel=xb.KERNEL_TCGEN05_I8)
+    dst = np.empty(want["dst"].size, np.float32)
+    conv.forward(src, dst)
+    assert np.array_equal(conv.forward_sums(), want["sums"])
+    assert np.array_equal(dst, want["dst"])
+    conv.close()
+
+
 def test_change_weights(oracle):
     case = [c for c in cases.ALL_CASES if c[0] == "mnist_24to48"][0]
     src, w = cases.make_inputs(case)
