@@ -79,6 +79,18 @@ xnor_nn_status_t xnor_nn_b200_synchronize(xnor_nn_resources_t res);
  * reports through the status code alone (src/status.cpp:3-15). */
 const char *xnor_nn_b200_last_error(void);
 
+/* xnor_nn_binarize_weights_float (src/binarize_weights_float.cpp:3-25: to = sign(from) *
+ * mean(from), the weights the Caffe layer's backward pass convolves with,
+ * external/caffe/src/caffe/layers/xnor_nn_conv_layer.cpp:97-98) for filter banks that live on the
+ * device, enqueued on `cuda_stream` without waiting. The mean is summed in one fixed shape, so
+ * repeated calls agree bit for bit; upstream's own sum is an OpenMP loop without a reduction
+ * clause and depends on the thread schedule. `to_device` may equal `from_device`. The upstream
+ * symbol itself takes this path (on the default stream, and waits) when both of its pointers are
+ * device memory. */
+xnor_nn_status_t xnor_nn_b200_binarize_weights_float(const xnor_nn_convolution_t *c,
+                                                     const float *from_device, float *to_device,
+                                                     void *cuda_stream);
+
 /* K = box filter of mean|x| (what the calculate_k executor computes into res[k]) for callers
  * that cannot allocate device memory when they need it: code that runs while a stream is being
  * captured into a CUDA graph, servers whose arena owns all device memory, sandboxed plugins.

@@ -74,6 +74,7 @@ def lib():
         L.xnor_nn_destroy_convolution.restype = None
         L.xnor_nn_binarize_weights_float.argtypes = [dp, C.c_void_p, C.c_void_p]
         L.xnor_nn_binarize_weights_float.restype = None
+        L.xnor_nn_b200_binarize_weights_float.argtypes = [dp, C.c_void_p, C.c_void_p, C.c_void_p]
         L.xnor_nn_b200_kernel_of.argtypes = [dp]
         L.xnor_nn_b200_forward.argtypes = [dp, rp]
         L.xnor_nn_b200_forward_sums.argtypes = [dp, rp, C.c_void_p]
@@ -160,8 +161,7 @@ class Convolution:
         try:
             _check(lib().xnor_nn_b200_forward(C.byref(self.c), self.res))
         finally:
-            self.res[SLOT_USER_SRC] = None
-            self.res[SLOT_USER_DST] = None
+            self._clear_user_io()
 
     def forward_stepwise(self, src, dst):
         """The literal upstream sequence: three executor calls through the function pointers."""
@@ -171,11 +171,16 @@ class Convolution:
             for ex in (self.c.binarize_data, self.c.calculate_k, self.c.forward):
                 _check(ex(C.addressof(self.c), self.res))
         finally:
-            self.res[SLOT_USER_SRC] = None
-            self.res[SLOT_USER_DST] = None
+            self._clear_user_io()
 
-    def binarize_weights_float(self, src, dst):
-        lib().xnor_nn_binarize_weights_float(C.byref(self.c), _ptr(src), _ptr(dst))
+    def binarize_weights_float(self, src, dst, stream=None):
+        """sign(src) * mean(src). Host arrays, or device tensors; with `stream` (device tensors
+        only) the work is enqueued there and not waited for."""
+        if stream is None:
+            lib().xnor_nn_binarize_weights_float(C.byref(self.c), _ptr(src), _ptr(dst))
+        else:
+            _check(lib().xnor_nn_b200_binarize_weights_float(C.byref(self.c), _ptr(src),
+                                                             _ptr(dst), stream))
 
     # -- single executors and extensions ---------------------------------------------------
     def execute(self, name, src=None, dst=None, weights=None):
@@ -224,6 +229,13 @@ class Convolution:
     def _set(self, slot, x):
         self._keep[slot] = x  # the library reads the pointer during the call: keep it alive
         self.res[slot] = _ptr(x)
+
+    def _clear_user_io(self):
+        # upstream's wrapper clears the two slots after every pass (include/xnor_nn.hpp:50-52);
+        # the references go too, so a caller's tensors are not held until the next call
+        for slot in (SLOT_USER_SRC, SLOT_USER_DST):
+            self.res[slot] = None
+            self._keep.pop(slot, None)
 
     def close(self):
         if getattr(self, "res", None) is not None and self._allocated:

@@ -439,13 +439,22 @@ xnor_nn_status_t xnor_nn_allocate_resources(const xnor_nn_convolution_t *c,
     return xnor_nn_success;
 }
 
-// Host helper of the training backward pass, upstream src/binarize_weights_float.cpp:3-25:
-// to = sign(from) * mean(from). Upstream sums with an unsynchronised OpenMP reduction; this
-// sums in index order, which is what upstream computes when run on one thread.
+// Helper of the training backward pass, upstream src/binarize_weights_float.cpp:3-25:
+// to = sign(from) * mean(from). Upstream sums with an unsynchronised OpenMP reduction, so its
+// result depends on the thread schedule. Host pointers: summed here in index order, which is
+// what upstream computes on one thread. Device pointers (both): the kernels of weights.cu on the
+// default stream, waited for, since the function cannot report anything and upstream returns
+// with `to` complete. One host and one device pointer is not supported.
 void xnor_nn_binarize_weights_float(const xnor_nn_convolution_t *c, const float *from,
                                     float *to) {
     if (!c || !from || !to) return;
     const int elems = c->oc * c->ic * c->kh * c->kw;
+    if (on_device(from) && on_device(to)) {
+        cudaError_t e = launch_binarize_weights_float(elems, from, to, nullptr);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+        if (e != cudaSuccess) (void)fail(e, "binarize_weights_float");
+        return;
+    }
     const float scale = 1.f / elems;
     float mean = 0.f;
     for (int i = 0; i < elems; i++) mean += from[i];
@@ -658,6 +667,17 @@ xnor_nn_status_t xnor_nn_b200_synchronize(xnor_nn_resources_t res) {
 }
 
 const char *xnor_nn_b200_last_error(void) { return t_last_error; }
+
+xnor_nn_status_t xnor_nn_b200_binarize_weights_float(const xnor_nn_convolution_t *c,
+                                                     const float *from_device, float *to_device,
+                                                     void *cuda_stream) {
+    if (!c || !from_device || !to_device) return xnor_nn_error_invalid_input;
+    if (!on_device(from_device) || !on_device(to_device)) return xnor_nn_error_invalid_input;
+    const long elems = (long)c->oc * c->ic * c->kh * c->kw;
+    if (elems <= 0) return xnor_nn_error_invalid_input;
+    CU(launch_binarize_weights_float(elems, from_device, to_device, (cudaStream_t)cuda_stream));
+    return xnor_nn_success;
+}
 
 long xnor_nn_b200_kernel_launches(void) { return g_kernel_launches.load(); }
 

@@ -66,6 +66,12 @@ cudaError_t launch_box_filter(const Plan &p, const float *a, float *k, cudaStrea
 cudaError_t launch_binarize_weights(const Plan &p, const float *w, void *bin_w, float *alpha,
                                     int32_t *op_c, cudaStream_t s);
 
+// to = sign(from) * mean(from) over `elems` device floats (upstream
+// src/binarize_weights_float.cpp:3-25), with a fixed summation shape. Takes and returns a few
+// hundred bytes of stream-ordered scratch.
+cudaError_t launch_binarize_weights_float(long elems, const float *from, float *to,
+                                          cudaStream_t s);
+
 // ---- convolution -----------------------------------------------------------------------------
 // dst = ((float)S * alpha) * K with S the signed agreement count over in-bounds taps
 // (upstream src/default/bcast_convolution_default.cpp:60-103). When `sums` is not null the raw

@@ -143,4 +143,65 @@ cudaError_t launch_binarize_weights(const Plan &p, const float *w, void *bin_w, 
     return cudaGetLastError();
 }
 
+// ---- float binarisation for the training backward pass ----------------------------------------
+// to = sign(from) * mean(from) over the whole filter bank (upstream
+// src/binarize_weights_float.cpp:3-25; the mean is of the signed values, as upstream has it).
+// Upstream accumulates the sum in an OpenMP loop without a reduction clause, so its result depends
+// on the thread schedule; here the sum has one fixed shape: thread t of block b adds elements
+// b*256 + t, + 65536, + 131072, ... in ascending order, a block folds its 256 running sums with
+// a fixed binary tree, and every block of the second kernel folds the 256 block sums with the
+// same tree. The result is therefore reproducible and within rounding of the one-thread sum.
+namespace {
+constexpr int kWfBlocks = 256, kWfThreads = 256;
+
+__device__ __forceinline__ float fold256(float v, float *sh) {
+    sh[threadIdx.x] = v;
+    __syncthreads();
+    for (int w = kWfThreads / 2; w > 0; w >>= 1) {
+        if ((int)threadIdx.x < w) sh[threadIdx.x] = __fadd_rn(sh[threadIdx.x], sh[threadIdx.x + w]);
+        __syncthreads();
+    }
+    return sh[0];
+}
+
+__global__ void __launch_bounds__(kWfThreads) wf_partial_kernel(const float *from, long elems,
+                                                                float *partial) {
+    __shared__ float sh[kWfThreads];
+    float acc = 0.f;
+    for (long i = (long)blockIdx.x * kWfThreads + threadIdx.x; i < elems;
+         i += (long)kWfBlocks * kWfThreads)
+        acc = __fadd_rn(acc, from[i]);
+    const float total = fold256(acc, sh);
+    if (threadIdx.x == 0) partial[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(kWfThreads) wf_scale_kernel(const float *from, float *to,
+                                                              long elems, const float *partial,
+                                                              float inv_elems) {
+    __shared__ float sh[kWfThreads];
+    const float mean = __fmul_rn(fold256(partial[threadIdx.x], sh), inv_elems);
+    for (long i = (long)blockIdx.x * kWfThreads + threadIdx.x; i < elems;
+         i += (long)gridDim.x * kWfThreads)
+        to[i] = __fmul_rn(from[i] >= .0f ? 1.f : -1.f, mean);
+}
+}  // namespace
+
+cudaError_t launch_binarize_weights_float(long elems, const float *from, float *to,
+                                          cudaStream_t s) {
+    float *partial = nullptr;
+    cudaError_t e = cudaMallocAsync(&partial, kWfBlocks * sizeof(float), s);
+    if (e != cudaSuccess) return e;
+    wf_partial_kernel<<<kWfBlocks, kWfThreads, 0, s>>>(from, elems, partial);
+    note_launch();
+    long blocks = (elems + kWfThreads - 1) / kWfThreads;
+    if (blocks > 1184) blocks = 1184;
+    if (blocks < 1) blocks = 1;
+    wf_scale_kernel<<<(unsigned)blocks, kWfThreads, 0, s>>>(from, to, elems, partial,
+                                                            1.f / (float)elems);
+    note_launch();
+    e = cudaGetLastError();
+    const cudaError_t f = cudaFreeAsync(partial, s);
+    return e != cudaSuccess ? e : f;
+}
+
 }  // namespace xb200
