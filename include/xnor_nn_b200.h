@@ -49,6 +49,25 @@ xnor_nn_b200_kernel_t xnor_nn_b200_kernel_of(const xnor_nn_convolution_t *c);
  * to the device once instead of twice, and the mean-|x| map is produced by the packing pass. */
 xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_resources_t res);
 
+/* Consecutive binary convolutions with no float tensor between them: layer i's results never
+ * leave the chip as floats; the convolution kernel writes their signs straight into layer i+1's
+ * packed input and their mean magnitude into its mean-|x| map, which is what layer i+1's
+ * binarize_data and calculate_k (src/bcast_binarize_data.cpp:43-73,
+ * src/bcast_calculate_k.cpp:49-66) would have derived from the stored floats. Upstream has no
+ * such call; it stands for what its Caffe model does with conv3 -> conv4 -> conv5
+ * (external/caffe/models/xnor_nn_alexnet/time.prototxt) minus the activation layers between them.
+ *   c[i], res[i]: the layers in order, each initialised, allocated and with binarize_weights done;
+ *   source: res[0][user_src]; result: res[layers-1][user_dst] (host or device memory);
+ *   layer i+1 must take what layer i produces: same mb, ic = oc, ih = oh, iw = ow, else
+ *   xnor_nn_error_invalid_input; every chained layer must run on the tensor-core kernels (unit
+ *   stride), else xnor_nn_unimplemented.
+ * The packed signs, hence every integer sum, equal those of calling the layers one after another;
+ * the mean-|x| maps of layers 1.. are summed in a fixed but not strictly sequential order, so the
+ * floats agree with the layer-by-layer result to rounding (about 1e-6 relative), reproducibly.
+ * All work is issued on the stream of res[0]. */
+xnor_nn_status_t xnor_nn_b200_forward_chain(int layers, const xnor_nn_convolution_t *const *c,
+                                            void **const *res);
+
 /* The convolution of the `forward` executor (src/default/bcast_convolution_default.cpp:60-91)
  * stopped before the alpha*K scaling: writes the signed agreement counts
  * S = 2*popcount(xnor) - op_c as int32, NCHW, mb*oc*oh*ow entries, to `sums` (host or device

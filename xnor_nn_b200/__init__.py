@@ -77,6 +77,7 @@ def lib():
         L.xnor_nn_b200_binarize_weights_float.argtypes = [dp, C.c_void_p, C.c_void_p, C.c_void_p]
         L.xnor_nn_b200_kernel_of.argtypes = [dp]
         L.xnor_nn_b200_forward.argtypes = [dp, rp]
+        L.xnor_nn_b200_forward_chain.argtypes = [C.c_int, C.POINTER(dp), C.POINTER(rp)]
         L.xnor_nn_b200_forward_sums.argtypes = [dp, rp, C.c_void_p]
         L.xnor_nn_b200_read_resource.argtypes = [dp, rp, C.c_int, C.c_void_p, C.c_size_t]
         L.xnor_nn_b200_set_stream.argtypes = [rp, C.c_void_p]
@@ -249,3 +250,18 @@ class Convolution:
             self.close()
         except Exception:
             pass
+
+
+def forward_chain(convs, src, dst):
+    """Runs `convs` (Convolution objects, in order) back to back without the float tensors
+    between them: src -> convs[0] -> ... -> convs[-1] -> dst."""
+    n = len(convs)
+    cs = (C.POINTER(ConvolutionDesc) * n)(*[C.pointer(cv.c) for cv in convs])
+    rs = (C.POINTER(C.c_void_p) * n)(*[C.cast(cv.res, C.POINTER(C.c_void_p)) for cv in convs])
+    convs[0]._set(SLOT_USER_SRC, src)
+    convs[-1]._set(SLOT_USER_DST, dst)
+    try:
+        _check(lib().xnor_nn_b200_forward_chain(n, cs, rs))
+    finally:
+        convs[0]._clear_user_io()
+        convs[-1]._clear_user_io()

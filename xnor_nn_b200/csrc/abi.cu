@@ -67,6 +67,7 @@ struct ResCtx {
     static constexpr int kMaxSlices = 8;
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t ev_in[kMaxSlices] = {}, ev_done[kMaxSlices] = {}, ev_edge = nullptr;
+    cudaEvent_t ev_chain = nullptr;  // orders this context's stream before a chained call
 };
 
 std::mutex g_mu;
@@ -390,6 +391,7 @@ void xnor_nn_free_resources(xnor_nn_resources_t res) {
             if (x->stage[i]) cudaFree(x->stage[i]);
         if (x->sums_stage) cudaFree(x->sums_stage);
         if (x->error_word) cudaFree(x->error_word);
+        if (x->ev_chain) cudaEventDestroy(x->ev_chain);
         if (x->copy_in) cudaStreamDestroy(x->copy_in);
         if (x->copy_out) cudaStreamDestroy(x->copy_out);
         for (int i = 0; i < ResCtx::kMaxSlices; i++) {
@@ -594,6 +596,90 @@ xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_re
     if (st != xnor_nn_success) return st;
     if (!direct)
         CU(cudaMemcpyAsync(user, dst, dst_elems(*p) * sizeof(float), cudaMemcpyDeviceToHost,
+                           x->stream));
+    if (!direct || staged) return sync_and_check(x);
+    return xnor_nn_success;
+}
+
+xnor_nn_status_t xnor_nn_b200_forward_chain(int layers, const xnor_nn_convolution_t *const *c,
+                                            void **const *res) {
+    if (layers < 1 || layers > 64 || !c || !res) return xnor_nn_error_invalid_input;
+    const Plan *plan[64];
+    ResCtx *ctx[64];
+    for (int i = 0; i < layers; i++) {
+        void **r = res[i];
+        if (!c[i] || !r || !r[xnor_nn_resource_bin_src] || !r[xnor_nn_resource_bin_weights] ||
+            !r[xnor_nn_resource_a] || !r[xnor_nn_resource_k] || !r[xnor_nn_resource_alpha] ||
+            !r[xnor_nn_resource_operations_count])
+            return xnor_nn_error_invalid_input;
+        plan[i] = plan_of(c[i]);
+        ctx[i] = find_ctx(r);
+        if (!plan[i] || !ctx[i] || ctx[i]->device != ctx[0]->device)
+            return xnor_nn_error_invalid_input;
+        if (!plan[i]->formats_ok) return xnor_nn_unimplemented;
+    }
+    void *user_src = res[0][xnor_nn_resource_user_src];
+    void *user_dst = res[layers - 1][xnor_nn_resource_user_dst];
+    if (!user_src || !user_dst) return xnor_nn_error_invalid_input;
+    for (int i = 0; i + 1 < layers; i++) {
+        const Plan &a = *plan[i], &b = *plan[i + 1];
+        if (a.mb != b.mb || a.oc != b.ic || a.oh != b.ih || a.ow != b.iw)
+            return xnor_nn_error_invalid_input;
+        if (a.family != kTcgen05 || b.family != kTcgen05) {
+            snprintf(t_last_error, sizeof t_last_error,
+                     "layers %d and %d cannot be chained: both must run on the %s kernels", i,
+                     i + 1, family_name(kTcgen05));
+            return xnor_nn_unimplemented;
+        }
+    }
+    if (layers == 1) return xnor_nn_b200_forward(c[0], res[0]);
+
+    ResCtx *x = ctx[0];
+    DeviceGuard dg(x->device);
+    log_exec(*plan[0], "chained forward");
+    // Everything runs on the first layer's stream; work the caller queued on the other layers'
+    // streams (their binarize_weights, for instance) is ordered in front of it.
+    for (int i = 1; i < layers; i++) {
+        if (ctx[i]->stream == x->stream) continue;
+        if (!ctx[i]->ev_chain)
+            CU(cudaEventCreateWithFlags(&ctx[i]->ev_chain, cudaEventDisableTiming));
+        CU(cudaEventRecord(ctx[i]->ev_chain, ctx[i]->stream));
+        CU(cudaStreamWaitEvent(x->stream, ctx[i]->ev_chain, 0));
+    }
+    const void *src = nullptr;
+    bool staged = false;
+    xnor_nn_status_t st = stage_in(x, 0, user_src, src_bytes(*plan[0]), &src, &staged);
+    if (st != xnor_nn_success) return st;
+    const Plan &last = *plan[layers - 1];
+    const bool direct = on_device(user_dst);
+    float *dst = (float *)user_dst;
+    if (!direct) {
+        st = ensure_stage(x, 2, dst_elems(last) * sizeof(float));
+        if (st != xnor_nn_success) return st;
+        dst = (float *)x->stage[2];
+    }
+    CU(launch_binarize_data(*plan[0], (const float *)src, res[0][xnor_nn_resource_bin_src],
+                            (float *)res[0][xnor_nn_resource_a], x->stream));
+    for (int i = 0; i < layers; i++) {
+        void **r = res[i];
+        ChainTarget next;
+        const bool emit = i + 1 < layers;
+        if (emit) {
+            const Plan &n = *plan[i + 1];
+            next.bin_src = res[i + 1][xnor_nn_resource_bin_src];
+            next.a = (float *)res[i + 1][xnor_nn_resource_a];
+            next.wp = n.wp; next.hp = n.hp; next.lead = n.lead; next.icp = n.icp;
+            next.inv_ic = n.inv_ic;
+        }
+        CU(launch_conv_tcgen05(*plan[i], r[xnor_nn_resource_bin_src],
+                               r[xnor_nn_resource_bin_weights],
+                               (const float *)r[xnor_nn_resource_alpha], nullptr,
+                               (const float *)r[xnor_nn_resource_a],
+                               (float *)r[xnor_nn_resource_k], emit ? nullptr : dst, nullptr,
+                               x->error_word, x->stream, emit ? &next : nullptr));
+    }
+    if (!direct)
+        CU(cudaMemcpyAsync(user_dst, dst, dst_elems(last) * sizeof(float), cudaMemcpyDeviceToHost,
                            x->stream));
     if (!direct || staged) return sync_and_check(x);
     return xnor_nn_success;

@@ -76,6 +76,12 @@ struct TcArgs {
     int n_ring;           // weight-ring depth
     uint32_t slab_chunk_bytes, slab_group_bytes, b_chunk_bytes, b_stage_bytes;
     uint32_t slab_tx_bytes, b_tx_bytes;  // bytes TMA writes per group / stage (the boxes)
+    // chained layers: instead of floats the epilogue writes the next layer's packed input
+    uint8_t *emit_bin;    // next layer's +-1 byte frame, or null
+    float *emit_a;        // next layer's mean-|x| map
+    int e_wp, e_hp, e_lead, e_icp;  // the next layer's frame geometry
+    float e_inv_ic;       // 1.f / (next layer's channels = this layer's filters)
+    int n_inner;          // 1: a CTA works through all filter tiles of a pixel tile in a row
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -198,6 +204,7 @@ struct __align__(16) Control {
     uint32_t tmem_base;
     int abort_flag;
     float alpha[kAlphaSmem];
+    float fold[2][4][kEpiWarps / 4][32];  // chained layers: per-warp partial sums of |y|
 };
 constexpr int kControlBytes = (sizeof(Control) + 1023) / 1024 * 1024;
 
@@ -214,22 +221,47 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *v) {
         : "r"(taddr));
 }
 
+// Which tile a CTA works on in its it-th round. Default: tiles are dealt round-robin with the
+// filter tile as the fast index. n_inner: pixel tiles are dealt round-robin and a CTA walks all
+// filter tiles of its pixel tile back to back (so that per-pixel state can be carried across
+// them in registers).
+__device__ __forceinline__ int tile_rounds(const TcArgs &g) {
+    if (g.n_inner) {
+        const int mine = (g.m_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+        return mine > 0 ? mine * g.n_tiles : 0;
+    }
+    const int total = g.m_tiles * g.n_tiles;
+    return (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+}
+__device__ __forceinline__ void tile_at(const TcArgs &g, int it, int &mt, int &nt) {
+    if (g.n_inner) {
+        const int r = it / g.n_tiles;
+        nt = it - r * g.n_tiles;
+        mt = (int)blockIdx.x + r * (int)gridDim.x;
+    } else {
+        const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+        mt = tile / g.n_tiles;
+        nt = tile - mt * g.n_tiles;
+    }
+}
+
 // ---- epilogue role (both kernels) ----------------------------------------------------------------
 // Warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); several warps share a quadrant and split
 // its columns between them.
 __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uint32_t tmem_base,
                                               int warp, int lane, bool alpha_in_smem) {
     volatile int *abort_flag = &ctl->abort_flag;
-    const int total_tiles = g.m_tiles * g.n_tiles;
+    const int rounds = tile_rounds(g);
     // Several warps share a quadrant and split its columns between them.
     const int quad = warp & 3;
     const int cgroup = (warp - 2) >> 2, cgroups = kEpiWarps / 4;
     const int frame = g.hp * g.wp;
     const long ohw = (long)g.oh * g.ow;
-    int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
-        const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
+    float run = 0.f;  // chained layers: running sum of |y| over the filter tiles of a pixel
+    for (int it = 0; ok && it < rounds; it++) {
+        int mt, nt;
+        tile_at(g, it, mt, nt);
         const int b = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         const long q = (long)mt * BM + quad * 32 + lane;
@@ -266,7 +298,63 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
-        if (!g.sums && !g.dst_nhwc) {
+        if (g.emit_bin) {
+            // Chained layers: y = (S * alpha) * K is not stored; its sign goes straight into the
+            // next layer's byte frame (+1 = 0x01, -1 = 0xFF, filters past the last one 0) and
+            // |y| / OC is summed into that layer's mean-|x| map. A thread owns one pixel and 32
+            // neighbouring filters = 32 contiguous bytes of the frame.
+            const float *al = alpha_in_smem ? ctl->alpha + oc0 : g.alpha + oc0;
+            uint8_t *row = g.emit_bin +
+                           ((long)g.e_lead + ((long)n * g.e_hp + oh) * g.e_wp + ow) * g.e_icp + oc0;
+            float part = 0.f;
+            for (int c0 = 32 * cgroup; c0 < g.n_tile; c0 += 32 * cgroups) {
+                uint32_t v[32];
+                const int width = g.n_tile - c0 >= 32 ? 32 : 16;
+                if (width == 32) {
+                    tc_ld32(taddr + (uint32_t)c0, v);
+                } else {
+#pragma unroll
+                    for (int j = 16; j < 32; j++) v[j] = 0;
+                    tc_ld16(taddr + (uint32_t)c0, v);
+                }
+                tc_wait_ld();
+                if (valid) {
+                    const int lim = min(n_valid - c0, width);
+                    uint32_t w[8];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        uint32_t word = 0;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            if (j + i < lim) {
+                                const float y = __fmul_rn(
+                                    __fmul_rn((float)(int)v[j + i], al[c0 + j + i]), kk);
+                                part = __fadd_rn(part, __fmul_rn(fabsf(y), g.e_inv_ic));
+                                word |= ((__float_as_uint(y) >> 31) ? 0xFFu : 0x01u) << (8 * i);
+                            }
+                        }
+                        w[j >> 2] = word;
+                    }
+                    if (oc0 + c0 + 16 <= g.e_icp)
+                        *reinterpret_cast<uint4 *>(row + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (width == 32 && oc0 + c0 + 32 <= g.e_icp)
+                        *reinterpret_cast<uint4 *>(row + c0 + 16) =
+                            make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+            // Fold the column groups' partial sums in a fixed order (group 0, 1, 2, 3, then the
+            // next filter tile), so the map is reproducible; the four warps of a lane quadrant
+            // meet on a named barrier of their own.
+            ctl->fold[it & 1][quad][cgroup][lane] = part;
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + quad), "r"(32 * (kEpiWarps / 4)) : "memory");
+            if (cgroup == 0) {
+                if (nt == 0) run = 0.f;
+#pragma unroll
+                for (int c = 0; c < kEpiWarps / 4; c++)
+                    run = __fadd_rn(run, ctl->fold[it & 1][quad][c][lane]);
+                if (nt == g.n_tiles - 1 && valid) g.emit_a[pix] = run;
+            }
+        } else if (!g.sums && !g.dst_nhwc) {
             // NCHW floats: for one filter the 32 lanes hold 32 neighbouring pixels, so a
             // store instruction writes one contiguous run.
             float *out = g.dst + ((long)n * g.oc + oc0) * ohw + r;
@@ -397,7 +485,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    const int total_tiles = g.m_tiles * g.n_tiles;
+    const int rounds = tile_rounds(g);
     const int ksteps = g.taps * g.chunks_per_tap;
     const uint32_t stage0 = smem_u32(stages);
 
@@ -409,8 +497,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             uint32_t armed = 0;  // bit s: stage s holds a load nobody is known to have consumed
             uint32_t armed_parity = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
+            for (int it = 0; ok && it < rounds; it++) {
+                int mt, nt;
+                tile_at(g, it, mt, nt);
                 int row = g.lead + mt * BM - g.ph * g.wp - g.pw;  // tap (0,0)
                 int brow = nt * g.n_tile;
                 int kw = 0, chunk = 0;
@@ -454,13 +543,12 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             // ---- MMA issuer: kept lean, a single thread feeds the tensor pipe ----
             int stage = 0;
             uint32_t phase = 0;
-            int it = 0;
             bool ok = true;
             const uint64_t hi = (uint64_t)g.desc_hi << 32;
             const uint32_t a_lo0 = ((stage0 >> 4) & 0x3FFF) | (1u << 16);
             const uint32_t b_lo0 = (((stage0 + g.a_bytes) >> 4) & 0x3FFF) | (1u << 16);
             const uint32_t stage_units = g.stage_bytes >> 4;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
+            for (int it = 0; ok && it < rounds; it++) {
                 const int b = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2);
@@ -565,7 +653,7 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
-    const int total_tiles = g.m_tiles * g.n_tiles;
+    const int rounds = tile_rounds(g);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -575,8 +663,9 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
             uint32_t armed = 0, armed_parity = 0;            // weight ring
             uint32_t slab_armed = 0, slab_armed_parity = 0;  // slab ring
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
+            for (int it = 0; ok && it < rounds; it++) {
+                int mt, nt;
+                tile_at(g, it, mt, nt);
                 const int row0 = g.lead + mt * BM - g.ph * g.wp - g.pw;  // first slab row
                 for (int cg = 0; ok && cg < g.groups_per_tile; cg++) {
                     // the slab of this chunk group
@@ -642,13 +731,12 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
             // ---- MMA issuer ----
             int stage = 0, slab = 0;
             uint32_t phase = 0, slab_phase = 0;
-            int it = 0;
             bool ok = true;
             const uint64_t hi = (uint64_t)g.desc_hi << 32;
             const uint32_t a_lo0 = ((slab0 >> 4) & 0x3FFF) | (1u << 16);
             const uint32_t b_lo0 = ((ring0 >> 4) & 0x3FFF) | (1u << 16);
             const uint32_t row_units = (uint32_t)g.kchunk >> 4;  // one slab row, 16-byte units
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, it++) {
+            for (int it = 0; ok && it < rounds; it++) {
                 const int b = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2);
@@ -791,7 +879,8 @@ bool encode_bytes_2d_uncached(CUtensorMap *map, const void *ptr, uint64_t rows, 
 
 cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *bin_w,
                                 const float *alpha, const float *k, const float *a, float *k_out,
-                                float *dst, int32_t *sums, int *error_word, cudaStream_t s) {
+                                float *dst, int32_t *sums, int *error_word, cudaStream_t s,
+                                const ChainTarget *next) {
     if (p.q_total == 0) return cudaSuccess;
     CUtensorMap map_a, map_b;
     if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk, BM) ||
@@ -811,6 +900,14 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.kw = p.kw; g.ph = p.ph; g.pw = p.pw; g.wp = p.wp; g.hp = p.hp; g.lead = p.lead;
     g.oh = p.oh; g.ow = p.ow; g.oc = p.oc; g.ocp16 = p.ocp16;
     g.dst_nhwc = p.dst_nhwc;
+    g.emit_bin = nullptr; g.emit_a = nullptr; g.n_inner = 0;
+    g.e_wp = g.e_hp = g.e_lead = g.e_icp = 0; g.e_inv_ic = 0.f;
+    if (next) {
+        g.emit_bin = (uint8_t *)next->bin_src; g.emit_a = next->a;
+        g.e_wp = next->wp; g.e_hp = next->hp; g.e_lead = next->lead; g.e_icp = next->icp;
+        g.e_inv_ic = next->inv_ic;
+        g.n_inner = 1;
+    }
     // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N and M encoded
     g.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.n_tile >> 3) << 17) |
               ((uint32_t)(BM >> 4) << 24);
@@ -888,7 +985,7 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     }
     if (!sm_count[d]) cudaDeviceGetAttribute(&sm_count[d], cudaDevAttrMultiProcessorCount, dev);
     const int sms = sm_count[d];
-    const int tiles = g.m_tiles * g.n_tiles;
+    const int tiles = g.n_inner ? g.m_tiles : g.m_tiles * g.n_tiles;
     const int grid = tiles < sms ? tiles : sms;
     note_launch();
     return launch_overlapped(kernel, dim3(grid), dim3(kThreads), smem, s, map_a, map_b, g);

@@ -85,8 +85,23 @@ cudaError_t launch_conv_popc(const Plan &p, const uint32_t *bin_src, const uint3
 // ran out; it is never cleared by the kernel. With k == nullptr the epilogue box-filters K from
 // the mean-|x| map `a` itself (same arithmetic as launch_box_filter) and records it in k_out,
 // which saves the separate stencil launch in the fused forward call.
+//
+// `next` chains two layers in the packed domain: instead of storing floats, the epilogue writes
+// the sign of every result into the following layer's byte frame and the mean |result| over the
+// filters into its mean-|x| map, which is what that layer's binarize_data and the first half of
+// its calculate_k would have produced from the stored floats (upstream
+// src/bcast_binarize_data.cpp:43-73, src/bcast_calculate_k.cpp:49-66). The signs are exact; the
+// mean is summed per group of filters and folded in a fixed order, so it is reproducible but
+// rounds differently from upstream's strictly sequential sum.
+struct ChainTarget {
+    void *bin_src;        // the next layer's res[bin_src]
+    float *a;             // the next layer's res[a]
+    int wp, hp, lead, icp;  // its frame geometry (Plan)
+    float inv_ic;         // its Plan::inv_ic
+};
 cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *bin_w,
                                 const float *alpha, const float *k, const float *a, float *k_out,
-                                float *dst, int32_t *sums, int *error_word, cudaStream_t s);
+                                float *dst, int32_t *sums, int *error_word, cudaStream_t s,
+                                const ChainTarget *next = nullptr);
 
 }  // namespace xb200
