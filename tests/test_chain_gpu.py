@@ -15,7 +15,7 @@ from xnor_nn_b200 import synth
 pytestmark = pytest.mark.gpu
 
 REL_TOL = 1e-4      # the float tolerance of the parity contract
-A_REL_TOL = 2e-6    # mean-|x| map: reordering of a sum of a few hundred non-negative terms
+A_REL_TOL = 1e-5    # mean-|x| map: a reordered sum of a few hundred non-negative terms
 
 
 def _layer(mb, ic, oc, ih, iw, k, pad, kernel=None):

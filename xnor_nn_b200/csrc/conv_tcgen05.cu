@@ -299,10 +299,12 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
         if (g.emit_bin) {
-            // Chained layers: y = (S * alpha) * K is not stored; its sign goes straight into the
-            // next layer's byte frame (+1 = 0x01, -1 = 0xFF, filters past the last one 0) and
-            // |y| / OC is summed into that layer's mean-|x| map. A thread owns one pixel and 32
-            // neighbouring filters = 32 contiguous bytes of the frame.
+            // Chained layers: y = (S * alpha) * K is not stored. alpha and K are never negative,
+            // so the sign bit of y is the sign bit of S: it goes straight into the next layer's
+            // byte frame (+1 = 0x01, -1 = 0xFF, filters past the last one 0). |y| summed over the
+            // filters and divided by their number is that layer's mean-|x| map; K is common to a
+            // pixel, so the sum runs over |S| * alpha and is scaled once at the end. A thread
+            // owns one pixel and 32 neighbouring filters = 32 contiguous bytes of the frame.
             const float *al = alpha_in_smem ? ctl->alpha + oc0 : g.alpha + oc0;
             uint8_t *row = g.emit_bin +
                            ((long)g.e_lead + ((long)n * g.e_hp + oh) * g.e_wp + ow) * g.e_icp + oc0;
@@ -321,19 +323,33 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
                 if (valid) {
                     const int lim = min(n_valid - c0, width);
                     uint32_t w[8];
+                    if (alpha_in_smem && lim >= 32) {
+                        const float4 *a4 = reinterpret_cast<const float4 *>(al + c0);
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        uint32_t word = 0;
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            if (j + i < lim) {
-                                const float y = __fmul_rn(
-                                    __fmul_rn((float)(int)v[j + i], al[c0 + j + i]), kk);
-                                part = __fadd_rn(part, __fmul_rn(fabsf(y), g.e_inv_ic));
-                                word |= ((__float_as_uint(y) >> 31) ? 0xFFu : 0x01u) << (8 * i);
-                            }
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 a = a4[j >> 2];
+                            part = fmaf(fabsf((float)(int)v[j]), a.x, part);
+                            part = fmaf(fabsf((float)(int)v[j + 1]), a.y, part);
+                            part = fmaf(fabsf((float)(int)v[j + 2]), a.z, part);
+                            part = fmaf(fabsf((float)(int)v[j + 3]), a.w, part);
+                            // byte 3 of each count, sign-replicated: 0xFF where S < 0, else 0
+                            const uint32_t lo = __byte_perm(v[j], v[j + 1], 0x00FB);
+                            const uint32_t hi = __byte_perm(v[j + 2], v[j + 3], 0x00FB);
+                            w[j >> 2] = __byte_perm(lo, hi, 0x5410) | 0x01010101u;
                         }
-                        w[j >> 2] = word;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            uint32_t word = 0;
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                if (j + i < lim) {
+                                    part = fmaf(fabsf((float)(int)v[j + i]), al[c0 + j + i], part);
+                                    word |= ((v[j + i] >> 31) ? 0xFFu : 0x01u) << (8 * i);
+                                }
+                            }
+                            w[j >> 2] = word;
+                        }
                     }
                     if (oc0 + c0 + 16 <= g.e_icp)
                         *reinterpret_cast<uint4 *>(row + c0) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -352,7 +368,8 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
 #pragma unroll
                 for (int c = 0; c < kEpiWarps / 4; c++)
                     run = __fadd_rn(run, ctl->fold[it & 1][quad][c][lane]);
-                if (nt == g.n_tiles - 1 && valid) g.emit_a[pix] = run;
+                if (nt == g.n_tiles - 1 && valid)
+                    g.emit_a[pix] = __fmul_rn(__fmul_rn(run, kk), g.e_inv_ic);
             }
         } else if (!g.sums && !g.dst_nhwc) {
             // NCHW floats: for one filter the 32 lanes hold 32 neighbouring pixels, so a
