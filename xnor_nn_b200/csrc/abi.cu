@@ -734,9 +734,11 @@ xnor_nn_status_t xnor_nn_b200_read_resource(const xnor_nn_convolution_t *c,
 xnor_nn_status_t xnor_nn_b200_set_stream(xnor_nn_resources_t res, void *cuda_stream) {
     ResCtx *x = find_ctx(res);
     if (!x) return xnor_nn_error_invalid_input;
+    cudaStream_t next = cuda_stream ? (cudaStream_t)cuda_stream : x->own_stream;
+    if (next == x->stream) return xnor_nn_success;  // nothing to order (and legal during capture)
     DeviceGuard dg(x->device);
-    CU(cudaStreamSynchronize(x->stream));
-    x->stream = cuda_stream ? (cudaStream_t)cuda_stream : x->own_stream;
+    CU(cudaStreamSynchronize(x->stream));  // work already issued finishes before the switch
+    x->stream = next;
     return xnor_nn_success;
 }
 

@@ -1,9 +1,26 @@
 #include "plan.hpp"
 
+#include <cuda_runtime.h>
+
 #include <cstdlib>
 #include <cstring>
 
 namespace xb200 {
+
+// SMs of the current device (148 on B200); the same figure when no device can be asked, so that
+// plans made on a machine without a GPU come out as they would on the target.
+static int sm_count() {
+    static const int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+            (void)cudaGetLastError();
+            v = 148;
+        }
+        return v;
+    }();
+    return n;
+}
 
 int div_up_i(int a, int b) { return (a + b - 1) / b; }
 
@@ -98,7 +115,18 @@ void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
         // possible: the kernel is bound by the instruction stream that issues the MMAs, whose
         // cost per instruction does not shrink with N (conv4 on 128 images: 32.9 us at N=128
         // against 26.7 us at N=256).
-        const int n_tiles = div_up_i(p->oc, 256);
+        // Exception: when the whole layer is fewer tiles than half the SMs (small minibatches,
+        // e.g. one GPU's share of a sharded batch), halving N doubles the SMs at work without
+        // adding a round of tiles; below N=128 the per-instruction cost eats the gain.
+        const int fewest = div_up_i(p->oc, 256);
+        int n_tiles = fewest;
+        const long m_tiles = (p->q_total + 127) / 128;
+        while (m_tiles * n_tiles * 2 <= sm_count() && div_up_i(p->oc, n_tiles * 2) >= 128)
+            n_tiles *= 2;
+        if (const char *e = getenv("XNOR_NN_B200_NTILES")) {  // tuning override
+            const int v = atoi(e);
+            if (v >= fewest && div_up_i(p->oc, v) >= 16) n_tiles = v;
+        }
         p->n_tile = div_up_i(div_up_i(p->oc, n_tiles), 16) * 16;
         p->ocp16 = p->n_tile * n_tiles;
         p->lead = p->ph * p->wp + p->pw;
