@@ -483,6 +483,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         mbar_init(smem_u32(&ctl->drain), 1);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the descriptors are launch parameters: fetch them while the predecessor still runs
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -490,13 +493,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Everything above touched only this CTA's own shared and tensor memory; from here on the
-    // kernel reads what earlier kernels of the stream produced.
-    dependency_wait();
+    // Everything above touched only this CTA's own shared and tensor memory and the launch
+    // parameters. What earlier kernels of the stream produced is read by the TMA producer and
+    // the epilogue warps, each after its own dependency_wait(); the MMA issuer reads shared
+    // memory only.
     const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
-    if (alpha_in_smem)
-        for (int i = threadIdx.x; i < g.ocp16; i += kThreads)
-            ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -509,6 +510,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     if (warp == 0) {
         if (lane == 0) {
             // ---- TMA producer ----
+            dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
             uint32_t armed = 0;  // bit s: stage s holds a load nobody is known to have consumed
@@ -603,6 +605,13 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         __syncwarp();
     } else {
+        // ---- epilogue warps: stage alpha among themselves, then drain accumulators ----
+        dependency_wait();
+        if (alpha_in_smem) {
+            for (int i = threadIdx.x - 64; i < g.ocp16; i += 32 * kEpiWarps)
+                ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
+            asm volatile("bar.sync %0, %1;" ::"r"(5), "r"(32 * kEpiWarps) : "memory");
+        }
         epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
@@ -652,6 +661,9 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
         mbar_init(smem_u32(&ctl->drain), 1);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the descriptors are launch parameters: fetch them while the predecessor still runs
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -659,13 +671,11 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Everything above touched only this CTA's own shared and tensor memory; from here on the
-    // kernel reads what earlier kernels of the stream produced.
-    dependency_wait();
+    // Everything above touched only this CTA's own shared and tensor memory and the launch
+    // parameters. What earlier kernels of the stream produced is read by the TMA producer and
+    // the epilogue warps, each after its own dependency_wait(); the MMA issuer reads shared
+    // memory only.
     const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
-    if (alpha_in_smem)
-        for (int i = threadIdx.x; i < g.ocp16; i += kThreads)
-            ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -675,6 +685,7 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
     if (warp == 0) {
         if (lane == 0) {
             // ---- TMA producer ----
+            dependency_wait();
             int stage = 0, slab = 0;
             uint32_t phase = 0, slab_phase = 0;
             uint32_t armed = 0, armed_parity = 0;            // weight ring
@@ -810,6 +821,13 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         __syncwarp();
     } else {
+        // ---- epilogue warps: stage alpha among themselves, then drain accumulators ----
+        dependency_wait();
+        if (alpha_in_smem) {
+            for (int i = threadIdx.x - 64; i < g.ocp16; i += 32 * kEpiWarps)
+                ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
+            asm volatile("bar.sync %0, %1;" ::"r"(5), "r"(32 * kEpiWarps) : "memory");
+        }
         epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
