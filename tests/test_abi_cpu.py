@@ -144,3 +144,23 @@ def test_no_cpu_fallback_without_a_device():
     assert all(res[i] is None for i in range(3, 9))
     assert xb.last_error() != ""
     xb.lib().xnor_nn_destroy_convolution(C.byref(c))
+
+
+def test_chain_and_device_helpers_reject_bad_arguments():
+    """Argument checks of the entry points that have no upstream counterpart happen before any
+    CUDA call, so they can be exercised without a device."""
+    L = xb.lib()
+    c = xb.ConvolutionDesc()
+    assert L.xnor_nn_init_convolution(C.byref(c), 1, 0, 2, 0, 2, 16, 8, 6, 6, 3, 3, 1, 1, 1, 1) == 0
+    res = (C.c_void_p * xb.N_SLOTS)()
+    cs = (C.POINTER(xb.ConvolutionDesc) * 1)(C.pointer(c))
+    rs = (C.POINTER(C.c_void_p) * 1)(C.cast(res, C.POINTER(C.c_void_p)))
+    assert L.xnor_nn_b200_forward_chain(0, cs, rs) == xb.ERROR_INVALID_INPUT
+    assert L.xnor_nn_b200_forward_chain(1, None, rs) == xb.ERROR_INVALID_INPUT
+    assert L.xnor_nn_b200_forward_chain(1, cs, rs) == xb.ERROR_INVALID_INPUT   # nothing allocated
+    w = np.ones(16 * 8 * 9, np.float32)
+    # host memory where device memory is required
+    assert L.xnor_nn_b200_binarize_weights_float(C.byref(c), w.ctypes.data, w.ctypes.data,
+                                                 None) == xb.ERROR_INVALID_INPUT
+    assert L.xnor_nn_b200_binarize_weights_float(C.byref(c), None, None, None) == xb.ERROR_INVALID_INPUT
+    L.xnor_nn_destroy_convolution(C.byref(c))
