@@ -210,7 +210,16 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
                     for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
                 }
             } else {
-                for (int j = 0; j < nc; j++) acc = __fadd_rn(acc, f_s[j * TPX + lane]);
+                // channel tail: same order, groups of 16 loads in flight while they fit
+                int j0 = 0;
+                for (; j0 + 16 <= nc; j0 += 16) {
+                    float t[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
+                }
+                for (; j0 < nc; j0++) acc = __fadd_rn(acc, f_s[j0 * TPX + lane]);
             }
         } else if (WITH_PACK) {
             // a warp writes one pixel per pass: 32 lanes x 4 bytes, one 128-byte line
