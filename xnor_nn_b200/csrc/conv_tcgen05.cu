@@ -351,11 +351,20 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
                             w[j >> 2] = word;
                         }
                     }
-                    if (oc0 + c0 + 16 <= g.e_icp)
-                        *reinterpret_cast<uint4 *>(row + c0) = make_uint4(w[0], w[1], w[2], w[3]);
-                    if (width == 32 && oc0 + c0 + 32 <= g.e_icp)
-                        *reinterpret_cast<uint4 *>(row + c0 + 16) =
-                            make_uint4(w[4], w[5], w[6], w[7]);
+                    if (width == 32 && oc0 + c0 + 32 <= g.e_icp && ((oc0 + c0) & 31) == 0) {
+                        // one whole 32-byte sector per thread in a single store
+                        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                     ::"l"(row + c0), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                                       "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                                     : "memory");
+                    } else {
+                        if (oc0 + c0 + 16 <= g.e_icp)
+                            *reinterpret_cast<uint4 *>(row + c0) =
+                                make_uint4(w[0], w[1], w[2], w[3]);
+                        if (width == 32 && oc0 + c0 + 32 <= g.e_icp)
+                            *reinterpret_cast<uint4 *>(row + c0 + 16) =
+                                make_uint4(w[4], w[5], w[6], w[7]);
+                    }
                 }
             }
             // Fold the column groups' partial sums in a fixed order (group 0, 1, 2, 3, then the
@@ -413,11 +422,27 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
             // are contiguous in the result: four 16-byte stores.
             float *out = g.dst + pix * g.oc + oc0;
             const float *al = alpha_in_smem ? ctl->alpha + oc0 : g.alpha + oc0;
+            // 256-bit stores need 32-byte alignment: rows and tiles that are multiples of 8
+            // floats on a result buffer aligned likewise
+            const bool wide = (g.oc & 7) == 0 && (oc0 & 7) == 0 && ((uintptr_t)g.dst & 31) == 0;
             for (int c0 = 16 * cgroup; c0 < g.n_tile; c0 += 16 * cgroups) {
                 uint32_t v[16];
                 tc_ld16(taddr + (uint32_t)c0, v);
                 tc_wait_ld();
-                if (valid) {
+                if (valid && wide && c0 + 16 <= n_valid) {
+                    // 16 results = two whole 32-byte sectors, one 256-bit store each
+                    float x[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        x[j] = __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk);
+#pragma unroll
+                    for (int h = 0; h < 16; h += 8)
+                        asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                     ::"l"(out + c0 + h), "f"(x[h]), "f"(x[h + 1]), "f"(x[h + 2]),
+                                       "f"(x[h + 3]), "f"(x[h + 4]), "f"(x[h + 5]), "f"(x[h + 6]),
+                                       "f"(x[h + 7])
+                                     : "memory");
+                } else if (valid) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4) {
                         if (c0 + j >= n_valid) break;  // oc and n_valid are multiples of 4
