@@ -56,6 +56,10 @@ FORMAT_CASES = [
     _c("fmt_nchw_oihw_nhwc", 2, 24, 37, 6, 7, 3, 3, ph=1, pw=1, fmt=(0, 0, 1)),
     _c("fmt_nhwc_hwio_nchw", 2, 24, 37, 6, 7, 3, 3, ph=1, pw=1, fmt=(1, 1, 0)),
     _c("fmt_nhwc_hwio_nhwc", 2, 24, 37, 6, 7, 3, 3, ph=1, pw=1, fmt=(1, 1, 1)),
+    # NHWC results whose rows are not whole 32-byte sectors (20 filters) or not even 16-byte
+    # aligned (13 filters): the narrower store paths of the tensor-core epilogue
+    _c("fmt_nhwc_dst_oc20", 2, 20, 37, 6, 7, 3, 3, ph=1, pw=1, fmt=(0, 0, 1)),
+    _c("fmt_nhwc_dst_oc13", 2, 13, 37, 6, 7, 3, 3, ph=1, pw=1, fmt=(0, 0, 1)),
 ]
 
 ALL_CASES = TAIL_CASES + SHAPE_CASES + FORMAT_CASES
