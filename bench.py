@@ -152,7 +152,7 @@ class ClockSampler:
 
 # ---- reference arm / CPU baseline ----------------------------------------------------------------
 
-def upstream_forward_seconds(L, mb, budget_s, steps=None, warmup=1):
+def upstream_forward_seconds(L, mb, budget_s, steps=None, warmup=1, threads=None):
     """Seconds per forward pass (binarize_data + calculate_k + forward, what upstream's
     Convolution::forward runs) of the unmodified upstream library, bcast algorithm, all host
     threads, on `mb` images of layer L. Timed like upstream's perf harness
@@ -160,7 +160,7 @@ def upstream_forward_seconds(L, mb, budget_s, steps=None, warmup=1):
     import ctypes as C
     from oracle.pyoracle import UpstreamRef, UpstreamConv
     ref = UpstreamRef()
-    host_threads()
+    host_threads(threads)
     cfg_name = [k for k, v in synth.CONFIGS.items() if v.name == L.name][0]
     src, w = synth.make_inputs(cfg_name, mb=mb)
     c = UpstreamConv()
@@ -190,14 +190,15 @@ def upstream_forward_seconds(L, mb, budget_s, steps=None, warmup=1):
     return float(np.sum(times)), steps
 
 
-def host_threads():
-    """OpenMP threads the upstream library will use: all cores this process may run on. (A
-    launcher such as torchrun exports OMP_NUM_THREADS=1 for its workers; the CPU arm is meant to
-    use the whole host, so the team size is set explicitly.)"""
+def host_threads(want=None):
+    """OpenMP threads the upstream library will use: all cores this process may run on, or
+    `want`. (A launcher such as torchrun exports OMP_NUM_THREADS=1 for its workers; the CPU arm is
+    meant to use the whole host, so the team size is set explicitly.)"""
     try:
         import ctypes
         omp = ctypes.CDLL("libgomp.so.1")
-        want = len(os.sched_getaffinity(0))
+        if want is None:
+            want = len(os.sched_getaffinity(0))
         omp.omp_set_num_threads(want)
         return omp.omp_get_max_threads()
     except OSError:
@@ -431,6 +432,13 @@ def run_ours(args, L, rank, world, local_rank):
                    "ms_per_step": total / steps * 1e3,
                    "sample": "full minibatch (%d images), %d passes, upstream bcast, "
                              "XNOR_NN_ISA=2" % (L.mb, steps)}
+            # the same library on one thread, on a few images (it scales with the image count)
+            few = min(L.mb, 8)
+            t1, n1 = upstream_forward_seconds(L, few, 0, steps=2, warmup=1, threads=1)
+            cpu["one_thread"] = {"value": binary_ops(L, few) / (t1 / n1) / 1e12, "unit": "TOPS",
+                                 "ms_per_step": t1 / n1 * 1e3 * (L.mb / few),
+                                 "sample": "%d of %d images, scaled" % (few, L.mb)}
+            host_threads()
 
     if rank == 0:
         print(json.dumps({
