@@ -32,7 +32,7 @@ def main(argv):
     bufs = [[torch.randn(mb * c * 169, device="cuda") for c in CHANNELS] for _ in range(sets)]
 
     def timed(fn):
-        for i in range(6):
+        for i in range(30):  # warm-up: clocks and caches settle
             fn(bufs[i % sets])
         torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -526,6 +526,10 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Every CTA of this grid is resident from the start, so a dependent grid may be launched as
+    // soon as all of them have got here: its CTAs move in as these exit (SMs with one tile fewer
+    // exit a round early) and set themselves up; they wait for this grid's results themselves.
+    dependency_release();
     const uint32_t tmem_base = ctl->tmem_base;
 
     const int rounds = tile_rounds(g);
@@ -640,7 +644,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
-    dependency_release();  // the next kernel may set up while this CTA winds down
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -704,6 +707,10 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Every CTA of this grid is resident from the start, so a dependent grid may be launched as
+    // soon as all of them have got here: its CTAs move in as these exit (SMs with one tile fewer
+    // exit a round early) and set themselves up; they wait for this grid's results themselves.
+    dependency_release();
     const uint32_t tmem_base = ctl->tmem_base;
     const int rounds = tile_rounds(g);
 
@@ -856,7 +863,6 @@ conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
         epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
-    dependency_release();  // the next kernel may set up while this CTA winds down
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
