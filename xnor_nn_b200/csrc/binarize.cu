@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
     // drain and set themselves up under this grid's tail (conv4 step 56.6 -> 55.5 us against
     // triggering at the end of the block). They wait for this grid's results themselves.
     dependency_release();
+    dependency_wait();  // nothing of an earlier kernel is read or overwritten before this
     const long px = (long)blockIdx.x * TPX + lane;
     const bool live = px < g.n_px;
     const int n = live ? (int)(px / g.hw) : 0;
@@ -322,10 +323,13 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
             }
             (void)cudaGetLastError();
         }
-        binarize_bytes_nchw_kernel<WITH_A, WITH_PACK>
-            <<<(unsigned)((g.n_px + TPX - 1) / TPX), TWARPS * 32, 0, s>>>(g);
         note_launch();
-        return cudaGetLastError();
+        // Launched with programmatic stream serialisation like the convolution: behind one of
+        // this library's kernels (which trigger early) the blocks become resident while it
+        // drains and wait in dependency_wait(); behind anything else nothing changes.
+        return launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK>,
+                                 dim3((unsigned)((g.n_px + TPX - 1) / TPX)), dim3(TWARPS * 32), 0,
+                                 s, g);
     }
     switch (p.family) {
         case kPopc: binarize_kernel<kBitsDense, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
