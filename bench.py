@@ -49,8 +49,8 @@ def parse():
                     help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-probe", action="store_true", help="skip the pipe-rate probe")
-    ap.add_argument("--no-graph", action="store_true",
-                    help="time plain library calls instead of CUDA-graph replays of them")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay the step from CUDA graphs instead of calling the library")
     return ap.parse_args()
 
 
@@ -288,12 +288,14 @@ def run_ours(args, L, rank, world, local_rank):
     def eager_step(i):
         conv.forward(d_src[i % sets], d_dst[i % sets])
 
-    # The step is two kernel launches behind a C call; replaying it from a CUDA graph (one graph
-    # per tensor set, captured once) takes the host out of the loop. The same kernels run either
-    # way; --no-graph times the plain calls.
+    # The step is two kernel launches behind a C call. --graph replays it from a CUDA graph (one
+    # per tensor set, captured once), which takes the host out of the loop; the same kernels run
+    # either way. Plain calls are the default because they are faster here: consecutive launches
+    # of one stream overlap their set-up with the predecessor's tail, consecutive graph launches
+    # do not (54.3 vs 55.4 us per step on conv4).
     graphs = None
     launches_per_step = None
-    if not args.no_graph:
+    if args.graph:
         for i in range(2):
             eager_step(i)
         torch.cuda.synchronize()
