@@ -22,14 +22,20 @@
 //               order and store; runs under the next tile's MMAs thanks to the second
 //               accumulator
 //
-// Two kernels share these roles. The slab kernel is the fast one: the nine (or KH*KW) shifted A
-// tiles of a position tile overlap almost entirely, so it loads the union once per channel
-// chunk (128 + (KH-1)*(IW+PW) + KW-1 rows, a "slab") and points each tap's matrix descriptor at
-// a row offset inside it (the swizzle is a function of the absolute shared-memory address, so a
-// descriptor may start at any row). Only the weights are streamed per tap, which cuts the
-// L2->shared traffic per tile by a third and leaves room for a deeper weight ring; with 48 KB
-// stages the ring was too shallow to cover the TMA latency. The per-tap kernel loads an A tile
-// per tap and serves the shapes whose slab does not fit.
+// Two kernels share these roles. The per-tap kernel loads an A tile and a weight tile per
+// pipeline stage (one filter tap x one channel chunk). The slab kernel uses that the KH*KW
+// shifted A tiles of a position tile overlap almost entirely: it loads their union once per group
+// of channel chunks (128 + (KH-1)*(IW+PW) + KW-1 rows, a "slab") and points each tap's matrix
+// descriptor at a row offset inside it (the swizzle is a function of the absolute shared-memory
+// address, so a descriptor may start at any row); only the weights are streamed per tap, several
+// chunks per stage. The launcher picks the slab kernel where that packs more MMAs into a stage
+// (narrow chunks: the 5x5 layer with 96 channels) and the per-tap kernel elsewhere, where the two
+// are within a few percent of each other.
+//
+// The epilogue has three forms: floats in NCHW (a warp store is one contiguous run of a filter
+// plane), floats in NHWC (a thread owns whole 32-byte sectors and writes them with 256-bit
+// stores), and, for chained layers, no floats at all: the sign byte of every result goes into the
+// next layer's frame and sum |result| into its mean-|x| map (ChainTarget in kernels.cuh).
 //
 // Every wait on an mbarrier is bounded in time: when the bound is hit the kernel records where
 // in *error, every role winds down, copies in flight are waited for (again bounded), tensor
