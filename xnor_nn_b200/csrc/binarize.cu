@@ -121,12 +121,12 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 //
 // A block of four warps owns 32 neighbouring pixels and walks the channels in chunks of 128.
 // All warps load (lane = pixel, warp w the w-th quarter of the chunk's channels, so a load
-// instruction reads one 128-byte line of a channel plane; 32 independent loads per thread, issued one chunk ahead so that they are in flight
-// while the previous chunk is consumed). |x|/IC goes to a float tile and the sign byte to a byte
+// instruction reads one 128-byte line of a channel plane; 32 independent loads per thread, issued
+// one chunk ahead so that they are in flight while the previous chunk is consumed). |x|/IC goes to a float tile and the sign byte to a byte
 // tile in shared memory. Warp 0 then adds the float tile up channel by channel, one lane per
 // pixel, which keeps upstream's summation order, while the other warps copy the byte tile out
-// as one coalesced 128-byte line per pixel. Blocks are small enough that the whole grid is resident
-// at once for the benchmark layers.
+// as one coalesced 128-byte line per pixel. Seven blocks are resident per SM (72 registers per
+// thread, and the shared-memory carve-out is sized to match).
 constexpr int TPX = 32;    // pixels per block
 constexpr int TCC = 128;   // channels per chunk
 constexpr int TLD = TCC + 4;
