@@ -16,16 +16,24 @@
 extern "C" {
 #endif
 
-/* Kernel family that consumes the packed operands. Upstream picks between its int16 and int32
- * word paths and its per-ISA kernels inside xnor_nn_init_convolution
- * (src/implementation.cpp:16-24, src/bcast_convolution.cpp:92-117); this is the same decision
- * for the GPU. `auto` honours the environment variable XNOR_NN_B200_KERNEL
- * (popc | mma_b1 | tcgen05_i8) and otherwise picks by shape. */
+/* Kernel that consumes the packed operands. Upstream picks between its int16 and int32 word
+ * paths and its per-ISA kernels inside xnor_nn_init_convolution (src/implementation.cpp:16-24,
+ * src/bcast_convolution.cpp:92-117); this is the same decision for the GPU. `auto` honours the
+ * environment variable XNOR_NN_B200_KERNEL (popc | tcgen05_i8 | tcgen05_i8_rows) and otherwise
+ * picks by shape. Both tcgen05 kernels read the same packed operands (+-1 bytes), so chained
+ * layers and single executors work with either.
+ * (The value 1 is not used: the mma.sync b1 path it once named was measured slower than the
+ * integer pipe and never built; a request for an unknown value is treated as `auto`.) */
 typedef enum {
     xnor_nn_b200_kernel_auto = -1,
-    xnor_nn_b200_kernel_popc = 0,       /* LOP3+POPC integer pipe; every shape and format     */
-    xnor_nn_b200_kernel_mma_b1 = 1,     /* mma.sync b1: measured slower than popc, served by popc */
-    xnor_nn_b200_kernel_tcgen05_i8 = 2  /* tcgen05.mma kind::i8 on +-1 bytes; unit stride     */
+    xnor_nn_b200_kernel_popc = 0,            /* LOP3+POPC integer pipe; every shape and format */
+    xnor_nn_b200_kernel_tcgen05_i8 = 2,      /* tcgen05.mma kind::i8, tiles of 128 frame
+                                                positions x up to 256 filters; unit stride,
+                                                padding smaller than the filter. Shapes it cannot
+                                                serve go to the rows kernel, then to popc. */
+    xnor_nn_b200_kernel_tcgen05_i8_rows = 3  /* tcgen05.mma kind::i8, tiles of 128 filters x
+                                                whole output rows of one image; unit stride,
+                                                rows of at most 256 pixels, any padding */
 } xnor_nn_b200_kernel_t;
 
 /* xnor_nn_init_convolution (src/common_convolution.cpp:9-63) with the kernel family stated.
@@ -91,7 +99,10 @@ xnor_nn_status_t xnor_nn_b200_set_stream(xnor_nn_resources_t res, void *cuda_str
 void *xnor_nn_b200_get_stream(xnor_nn_resources_t res);
 
 /* Blocks until everything issued for `res` has finished. Calls that were given host pointers
- * have already waited; this is for callers that pass device pointers. */
+ * have already waited; this is for callers that pass device pointers, and it is the call that
+ * tells them of a kernel that gave up on one of its bounded waits (a call with device pointers
+ * only enqueues work and returns success): xnor_nn_unimplemented then, the place in
+ * xnor_nn_b200_last_error(), and the results since the previous synchronising call are invalid. */
 xnor_nn_status_t xnor_nn_b200_synchronize(xnor_nn_resources_t res);
 
 /* Text of the most recent CUDA failure seen by the calling thread ("" if none). Upstream
@@ -127,6 +138,38 @@ xnor_nn_status_t xnor_nn_b200_calculate_k_noalloc(const xnor_nn_convolution_t *c
                                                   void *cuda_stream);
 long xnor_nn_b200_noalloc_max_pixels(void);
 const char *xnor_nn_b200_noalloc_last_error(void);
+
+/* One forward pass (binarize_data, calculate_k, forward) of a host minibatch spread over several
+ * GPUs of this machine. Upstream serves the whole minibatch with a single Convolution::forward
+ * (include/xnor_nn.hpp:45-53) whose executors spread the images over all cores, the minibatch
+ * being their outermost loop (src/default/bcast_convolution_default.cpp:60-64); here device i of
+ * `n_devices` takes images [mb*i/n, mb*(i+1)/n), a contiguous slice, through its own upload /
+ * kernel / download pipeline, and the results land in the caller's one res[user_dst]: no peer
+ * access, no collective, the gather is the downloads.
+ *   res[user_src], res[user_dst]: host memory (pinned memory lets the devices' transfers overlap;
+ *   pageable memory works but serialises them);
+ *   res[user_weights]: host memory, needed when the device list is new (each device packs the
+ *   weights for itself and keeps them); when it is non-NULL on a later call the weights are
+ *   packed again, so clear the slot between passes as upstream's wrapper clears its slots;
+ *   devices: CUDA ordinals, no repeats; n_devices = 0 releases the per-device replicas (so does
+ *   xnor_nn_free_resources). `c`/`res` must have been initialised and allocated as usual (on any
+ *   device); the call does not touch their internal slots.
+ * Errors: a device ordinal that is not present, device pointers in the user slots ->
+ * xnor_nn_error_invalid_input; allocation failure on a device -> xnor_nn_error_memory. */
+xnor_nn_status_t xnor_nn_b200_forward_sharded(const xnor_nn_convolution_t *c,
+                                              xnor_nn_resources_t res, const int *devices,
+                                              int n_devices);
+
+/* Test hook for the kernels' failure detection; not for production use. Runs the convolution of
+ * the `forward` executor on res (tensor-core kernels only, res[user_dst] device memory) with the
+ * kernels' wait limit shortened to `wait_ms` milliseconds (1..1000) while one thread block leaves
+ * out the signal that publishes its first result tile. The warps waiting for that tile give up
+ * when the limit expires, the whole kernel winds down and returns by itself, and the call reports
+ * what every synchronising call reports after a give-up: xnor_nn_unimplemented, with the place
+ * in xnor_nn_b200_last_error(). res[user_dst] holds garbage afterwards; the resources stay
+ * usable. No upstream counterpart (upstream cannot time out). */
+xnor_nn_status_t xnor_nn_b200_selftest_lost_commit(const xnor_nn_convolution_t *c,
+                                                   xnor_nn_resources_t res, unsigned wait_ms);
 
 /* Number of kernels this library has launched in this process, for benchmark accounting. */
 long xnor_nn_b200_kernel_launches(void);

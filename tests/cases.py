@@ -48,6 +48,14 @@ SHAPE_CASES = [
     _c("one_by_one", 2, 40, 130, 7, 7, 1, 1),
     _c("single_pixel_out", 1, 8, 33, 3, 3, 3, 3),
     _c("oc260_two_filter_tiles", 1, 260, 16, 6, 6, 3, 3, ph=1, pw=1),
+    # padding as large as the filter or larger: outputs that see no input pixel at all are 0
+    _c("pad_ge_filter_1x1", 2, 24, 20, 5, 6, 1, 1, ph=1, pw=1),
+    _c("pad_ge_filter_3x3", 1, 16, 40, 4, 5, 3, 3, ph=3, pw=3),
+    # many small tiles: more work units than SMs, so CTAs of the persistent tensor-core kernels
+    # run several tiles back to back (both accumulators, wrapped pipeline phases), and a thin
+    # last round, which the image-row kernel cuts into half tiles
+    _c("split_tail_152_tiles", 38, 512, 8, 4, 4, 3, 3, ph=1, pw=1),
+    _c("three_rounds_450_tiles", 150, 384, 8, 2, 2, 3, 3, ph=1, pw=1),
 ]
 
 # Tensor formats other than NCHW/OIHW/NCHW

@@ -15,7 +15,7 @@ from xnor_nn_b200 import synth
 pytestmark = pytest.mark.gpu
 
 REL_TOL = 1e-4  # the float tolerance of the parity contract
-KERNELS = [xb.KERNEL_POPC, xb.KERNEL_MMA_B1, xb.KERNEL_TCGEN05_I8]
+KERNELS = [xb.KERNEL_POPC, xb.KERNEL_TCGEN05_I8, xb.KERNEL_TCGEN05_I8_ROWS]
 
 
 def _conv(case, kernel, weights):
@@ -97,21 +97,47 @@ def test_device_pointers_skip_staging(oracle, kernel):
 
 
 def test_host_pipeline_with_uneven_slices(oracle):
-    """Host buffers of 16 or more images go through the sliced upload/compute/download
-    pipeline; 17 images split into two unequal slices."""
-    L = synth.layer_shape("A", mb=17)._replace(oc=32)
-    src, w = synth.make_inputs("A", mb=17)
+    """Host buffers of 8 MB or more go through the sliced upload/compute/download pipeline;
+    41 images (10.6 MB) split into two unequal slices."""
+    mb = 41
+    L = synth.layer_shape("A", mb=mb)._replace(oc=32)
+    src, w = synth.make_inputs("A", mb=mb)
     w = np.ascontiguousarray(w[:32])
     from oracle.pyoracle import Shape
     want = oracle.convolution(
         Shape.make(L.mb, L.oc, L.ic, L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw), src, w)
-    for kernel in (xb.KERNEL_TCGEN05_I8, xb.KERNEL_POPC):
+    for kernel in KERNELS:
         conv = xb.Convolution(xb.ALGORITHM_BCAST, xb.NCHW, xb.OIHW, xb.NCHW, L.mb, L.oc, L.ic,
                               L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, w, kernel=kernel)
         dst = np.full(want["dst"].size, np.nan, np.float32)
         conv.forward(src, dst)
         assert np.array_equal(dst, want["dst"])
         assert np.array_equal(conv.read(xb.SLOT_K, np.float32), want["k"])
+        conv.close()
+
+
+def test_three_call_sequence_uploads_once(oracle):
+    """Upstream's literal sequence with host buffers: binarize_data leaves the mean-|x| map of
+    what it staged, the calculate_k that follows only box-filters it, and a calculate_k on its
+    own (or on another tensor) still computes everything itself."""
+    case = [c for c in cases.ALL_CASES if c[0] == "alexnet_conv4_affine"][0]
+    src, w = cases.make_inputs(case)
+    want = oracle.convolution(cases.oracle_shape(case), src, w)
+    for kernel in KERNELS:
+        conv = _conv(case, kernel, w)
+        dst = np.full(want["dst"].size, np.nan, np.float32)
+        conv.forward_stepwise(src, dst)
+        assert np.array_equal(dst, want["dst"])
+        assert np.array_equal(conv.read(xb.SLOT_A, np.float32), want["a"])
+        # calculate_k alone, on a different tensor at a different address
+        other = np.ascontiguousarray(src[::-1])
+        assert conv.execute("calculate_k", src=other) == xb.SUCCESS
+        want_other = oracle.convolution(cases.oracle_shape(case), other, w)
+        assert np.array_equal(conv.read(xb.SLOT_K, np.float32), want_other["k"])
+        # binarize_data then calculate_k on ANOTHER pointer: no shortcut
+        assert conv.execute("binarize_data", src=src) == xb.SUCCESS
+        assert conv.execute("calculate_k", src=other) == xb.SUCCESS
+        assert np.array_equal(conv.read(xb.SLOT_A, np.float32), want_other["a"])
         conv.close()
 
 
@@ -229,18 +255,35 @@ FULL = ["B", "C", "D", "E"]
 
 @pytest.mark.parametrize("cfg", FULL)
 def test_full_size_properties(oracle, cfg):
-    """At the benchmark sizes: (1) all kernel families agree bit for bit on the integer sums,
-    (2) the sums have the parity and range the operand count dictates, (3) negating the
-    weights negates every sum, (4) a slice of images checked against the oracle."""
+    """At the benchmark sizes: (1) all kernels agree bit for bit on the integer sums, (2) the
+    sums have the parity and range the operand count dictates, (3) negating the weights negates
+    every sum, (4) for every kernel the first two and the last image are checked against the
+    oracle: integer sums, mean-|x| and K maps bit for bit, scaled floats within 1e-4."""
     L = synth.CONFIGS[cfg]
     src, w = synth.make_inputs(cfg)
     ref_sums = None
     for kernel in KERNELS:
         conv = xb.Convolution(xb.ALGORITHM_BCAST, xb.NCHW, xb.OIHW, xb.NCHW, L.mb, L.oc, L.ic,
                               L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, w, kernel=kernel)
-        dst = np.empty(int(np.prod(conv.out_shape)), np.float32)
+        dst = np.full(int(np.prod(conv.out_shape)), np.nan, np.float32)
         conv.forward(src, dst)
         sums = conv.forward_sums()
+        # floats, A and K at full size: the three oracle-checked images (1e-4 relative for the
+        # results, bit for bit for the scale maps), and no result left unwritten anywhere
+        assert not np.isnan(dst).any()
+        from oracle.pyoracle import Shape
+        a_map = conv.read(xb.SLOT_A, np.float32)
+        k_map = conv.read(xb.SLOT_K, np.float32)
+        for first in (0, L.mb - 1):
+            n = 2 if first == 0 else 1
+            s = Shape.make(n, L.oc, L.ic, L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw)
+            want = oracle.convolution(s, src[first:first + n], w)
+            per = L.oc * conv.c.oh * conv.c.ow
+            _assert_close(dst[first * per:(first + n) * per], want["dst"])
+            pa, pk = L.ih * L.iw, conv.c.oh * conv.c.ow
+            assert np.array_equal(a_map[first * pa:(first + n) * pa], want["a"])
+            assert np.array_equal(k_map[first * pk:(first + n) * pk], want["k"])
+            assert np.array_equal(sums[first * per:(first + n) * per], want["sums"])
         if ref_sums is None:
             ref_sums = sums
             op_c = conv.read(xb.SLOT_OPERATIONS_COUNT, np.int32)
@@ -250,14 +293,6 @@ def test_full_size_properties(oracle, cfg):
             conv.change_weights(np.ascontiguousarray(-w))
             conv.forward(src, dst)
             assert np.array_equal(conv.forward_sums(), -sums)
-            # oracle on the first two and the last image
-            from oracle.pyoracle import Shape
-            for first in (0, L.mb - 1):
-                n = 2 if first == 0 else 1
-                s = Shape.make(n, L.oc, L.ic, L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw)
-                want = oracle.sums(s, src[first:first + n], w)
-                per = L.oc * conv.c.oh * conv.c.ow
-                assert np.array_equal(sums[first * per:(first + n) * per], want)
         else:
             assert np.array_equal(sums, ref_sums), xb.KERNEL_NAMES[kernel]
         conv.close()

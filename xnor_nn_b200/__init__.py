@@ -24,8 +24,9 @@ NCHW, NHWC, OIHW, HWIO = 0, 1, 2, 3
 (SLOT_USER_SRC, SLOT_USER_WEIGHTS, SLOT_USER_DST, SLOT_ALPHA, SLOT_BIN_SRC, SLOT_BIN_WEIGHTS,
  SLOT_A, SLOT_K, SLOT_OPERATIONS_COUNT) = range(9)
 N_SLOTS = 9
-KERNEL_AUTO, KERNEL_POPC, KERNEL_MMA_B1, KERNEL_TCGEN05_I8 = -1, 0, 1, 2
-KERNEL_NAMES = {KERNEL_POPC: "popc", KERNEL_MMA_B1: "mma_b1", KERNEL_TCGEN05_I8: "tcgen05_i8"}
+KERNEL_AUTO, KERNEL_POPC, KERNEL_TCGEN05_I8, KERNEL_TCGEN05_I8_ROWS = -1, 0, 2, 3
+KERNEL_NAMES = {KERNEL_POPC: "popc", KERNEL_TCGEN05_I8: "tcgen05_i8",
+                KERNEL_TCGEN05_I8_ROWS: "tcgen05_i8_rows"}
 
 _EXECUTOR = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_void_p))
 
@@ -86,6 +87,8 @@ def lib():
         L.xnor_nn_b200_synchronize.argtypes = [rp]
         L.xnor_nn_b200_last_error.restype = C.c_char_p
         L.xnor_nn_b200_kernel_launches.restype = C.c_long
+        L.xnor_nn_b200_forward_sharded.argtypes = [dp, rp, C.POINTER(C.c_int), C.c_int]
+        L.xnor_nn_b200_selftest_lost_commit.argtypes = [dp, rp, C.c_uint]
         L.xnor_nn_b200_calculate_k_noalloc.argtypes = [dp, C.c_void_p, C.c_void_p, C.c_void_p]
         L.xnor_nn_b200_noalloc_max_pixels.restype = C.c_long
         L.xnor_nn_b200_noalloc_last_error.restype = C.c_char_p
@@ -163,6 +166,21 @@ class Convolution:
             _check(lib().xnor_nn_b200_forward(C.byref(self.c), self.res))
         finally:
             self._clear_user_io()
+
+    def forward_sharded(self, src, dst, devices, weights=None):
+        """One pass of a host minibatch over several GPUs; `weights` (host array) is needed the
+        first time a device list is used."""
+        self._set(SLOT_USER_SRC, src)
+        self._set(SLOT_USER_DST, dst)
+        if weights is not None:
+            self._set(SLOT_USER_WEIGHTS, weights)
+        dev = (C.c_int * len(devices))(*devices)
+        try:
+            _check(lib().xnor_nn_b200_forward_sharded(C.byref(self.c), self.res, dev, len(devices)))
+        finally:
+            self._clear_user_io()
+            self.res[SLOT_USER_WEIGHTS] = None
+            self._keep.pop(SLOT_USER_WEIGHTS, None)
 
     def forward_stepwise(self, src, dst):
         """The literal upstream sequence: three executor calls through the function pointers."""

@@ -63,12 +63,31 @@ struct ResCtx {
     int32_t *sums_stage = nullptr;
     size_t sums_bytes = 0;
     int *error_word = nullptr;  // device int: set by a kernel whose bounded wait ran out
+    int *error_host = nullptr;  // pinned copy of it, refreshed by every synchronising call
+    // What exec_binarize_data staged from a host source, for the calculate_k that follows it
+    // (upstream's wrapper always calls the two back to back on one tensor,
+    // include/xnor_nn.hpp:45-53): the caller's pointer, and whether res[a] already holds the
+    // mean-|x| map of exactly that upload.
+    const void *staged_src_user = nullptr;
+    bool staged_a_valid = false;
+    struct Shard;               // per-device replicas used by xnor_nn_b200_forward_sharded
+    Shard *shards = nullptr;
+    int n_shards = 0;
     // host-pointer pipeline: copy engines on their own streams, events to chain the slices
     static constexpr int kMaxSlices = 8;
+    static constexpr size_t kSliceBytes = 4u << 20;  // smallest upload worth a slice of its own
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t ev_in[kMaxSlices] = {}, ev_done[kMaxSlices] = {}, ev_edge = nullptr;
     cudaEvent_t ev_chain = nullptr;  // orders this context's stream before a chained call
 };
+
+struct ResCtx::Shard {
+    int device = 0;
+    int first = 0, count = 0;  // its images of the whole minibatch
+    xnor_nn_convolution_t c = {};
+    void *res[xnor_nn_resource_number] = {};
+};
+void free_shards(ResCtx *x);
 
 std::mutex g_mu;
 std::unordered_map<const void *, ResCtx *> g_ctx;
@@ -92,6 +111,20 @@ struct DeviceGuard {
     }
 };
 
+// Where a caller's pointer lives: host memory (to be staged), memory of `device` (used in
+// place), or memory of another GPU (refused: the kernels run on the context's device and no peer
+// access is set up).
+enum Where { kHost, kHere, kElsewhere };
+Where where_is(const void *p, int device) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return kHost;
+    }
+    if (at.type == cudaMemoryTypeManaged) return kHere;
+    if (at.type != cudaMemoryTypeDevice) return kHost;
+    return at.device == device ? kHere : kElsewhere;
+}
 bool on_device(const void *p) {
     cudaPointerAttributes at;
     if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
@@ -99,6 +132,11 @@ bool on_device(const void *p) {
         return false;
     }
     return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+xnor_nn_status_t wrong_device(const char *what) {
+    snprintf(t_last_error, sizeof t_last_error,
+             "%s lives on another GPU than the resources it is used with", what);
+    return xnor_nn_error_invalid_input;
 }
 
 xnor_nn_status_t ensure_stage(ResCtx *x, int which, size_t bytes) {
@@ -114,7 +152,9 @@ xnor_nn_status_t ensure_stage(ResCtx *x, int which, size_t bytes) {
 // Device view of a read-only user tensor: the pointer itself, or a staged copy.
 xnor_nn_status_t stage_in(ResCtx *x, int which, const void *user, size_t bytes,
                           const void **dev, bool *staged) {
-    if (on_device(user)) {
+    const Where w = where_is(user, x->device);
+    if (w == kElsewhere) return wrong_device(which == 1 ? "the weights tensor" : "the source tensor");
+    if (w == kHere) {
         *dev = user;
         return xnor_nn_success;
     }
@@ -126,15 +166,20 @@ xnor_nn_status_t stage_in(ResCtx *x, int which, const void *user, size_t bytes,
     return xnor_nn_success;
 }
 
-// Waits for the context's stream and turns a kernel-side give-up into a status code.
+// Waits for the context's stream and turns a kernel-side give-up into a status code. The error
+// word comes back through pinned memory on the same stream, so the call synchronises once.
+// A give-up is reported as xnor_nn_unimplemented (upstream has no status for "the device did not
+// answer"); xnor_nn_b200_last_error() names the wait that ran out.
 xnor_nn_status_t sync_and_check(ResCtx *x) {
+    CU(cudaMemcpyAsync(x->error_host, x->error_word, sizeof(int), cudaMemcpyDeviceToHost,
+                       x->stream));
     CU(cudaStreamSynchronize(x->stream));
-    int word = 0;
-    CU(cudaMemcpy(&word, x->error_word, sizeof(int), cudaMemcpyDeviceToHost));
+    const int word = *x->error_host;
     if (word != 0) {
         snprintf(t_last_error, sizeof t_last_error,
                  "a kernel gave up waiting (site %d); results of this call are invalid", word);
-        CU(cudaMemset(x->error_word, 0, sizeof(int)));
+        CU(cudaMemsetAsync(x->error_word, 0, sizeof(int), x->stream));
+        *x->error_host = 0;
         return xnor_nn_unimplemented;
     }
     return xnor_nn_success;
@@ -193,11 +238,22 @@ xnor_nn_status_t exec_binarize_data(const xnor_nn_convolution_t *c, xnor_nn_reso
     log_exec(*p, "binarize_data");
     const void *src = nullptr;
     bool staged = false;
+    x->staged_src_user = nullptr;
+    x->staged_a_valid = false;
     xnor_nn_status_t st = stage_in(x, 0, res[xnor_nn_resource_user_src], src_bytes(*p), &src, &staged);
     if (st != xnor_nn_success) return st;
-    CU(launch_binarize_data(*p, (const float *)src, res[xnor_nn_resource_bin_src], nullptr,
-                            x->stream));
-    if (staged) CU(cudaStreamSynchronize(x->stream));
+    // A host source has just crossed PCIe: let the packing pass also leave the mean-|x| map in
+    // res[a], so that the calculate_k that follows (upstream's call order) needs neither a second
+    // upload nor a second pass over the source.
+    float *a = staged ? (float *)res[xnor_nn_resource_a] : nullptr;
+    CU(launch_binarize_data(*p, (const float *)src, res[xnor_nn_resource_bin_src], a, x->stream));
+    if (staged) {
+        CU(cudaStreamSynchronize(x->stream));
+        if (a) {
+            x->staged_src_user = res[xnor_nn_resource_user_src];
+            x->staged_a_valid = true;
+        }
+    }
     return xnor_nn_success;
 }
 
@@ -212,11 +268,21 @@ xnor_nn_status_t exec_calculate_k(const xnor_nn_convolution_t *c, xnor_nn_resour
     if (!p->formats_ok) return xnor_nn_unimplemented;
     DeviceGuard dg(x->device);
     log_exec(*p, "calculate_k");
-    const void *src = nullptr;
+    // The mean-|x| map of this very tensor is already in res[a] when binarize_data staged it a
+    // moment ago (same host pointer, no call in between): only the box filter is left. The
+    // shortcut is good for one call; a source changed in place between binarize_data and
+    // calculate_k would not be seen, which upstream's callers never do.
+    const bool reuse = x->staged_a_valid && x->staged_src_user == res[xnor_nn_resource_user_src];
+    x->staged_src_user = nullptr;
+    x->staged_a_valid = false;
     bool staged = false;
-    xnor_nn_status_t st = stage_in(x, 0, res[xnor_nn_resource_user_src], src_bytes(*p), &src, &staged);
-    if (st != xnor_nn_success) return st;
-    CU(launch_mean_abs(*p, (const float *)src, (float *)res[xnor_nn_resource_a], x->stream));
+    if (!reuse) {
+        const void *src = nullptr;
+        xnor_nn_status_t st =
+            stage_in(x, 0, res[xnor_nn_resource_user_src], src_bytes(*p), &src, &staged);
+        if (st != xnor_nn_success) return st;
+        CU(launch_mean_abs(*p, (const float *)src, (float *)res[xnor_nn_resource_a], x->stream));
+    }
     CU(launch_box_filter(*p, (const float *)res[xnor_nn_resource_a],
                          (float *)res[xnor_nn_resource_k], x->stream));
     if (staged) CU(cudaStreamSynchronize(x->stream));
@@ -236,6 +302,16 @@ xnor_nn_status_t run_conv(const Plan &p, ResCtx *x, xnor_nn_resources_t res, flo
                                 x->stream));
             return xnor_nn_success;
         case kTcgen05:
+            if (p.img) {
+                CU(launch_conv_tcgen05_img(p, res[xnor_nn_resource_bin_src],
+                                           res[xnor_nn_resource_bin_weights],
+                                           (const float *)res[xnor_nn_resource_alpha],
+                                           fuse_k ? nullptr : (const float *)res[xnor_nn_resource_k],
+                                           (const float *)res[xnor_nn_resource_a],
+                                           (float *)res[xnor_nn_resource_k], dst, sums,
+                                           x->error_word, x->stream));
+                return xnor_nn_success;
+            }
             CU(launch_conv_tcgen05(p, res[xnor_nn_resource_bin_src],
                                    res[xnor_nn_resource_bin_weights],
                                    (const float *)res[xnor_nn_resource_alpha],
@@ -264,8 +340,11 @@ xnor_nn_status_t exec_forward(const xnor_nn_convolution_t *c, xnor_nn_resources_
     if (!p->formats_ok) return xnor_nn_unimplemented;
     DeviceGuard dg(x->device);
     log_exec(*p, "forward");
+    x->staged_a_valid = false;
     void *user = res[xnor_nn_resource_user_dst];
-    const bool direct = on_device(user);
+    const Where w = where_is(user, x->device);
+    if (w == kElsewhere) return wrong_device("the result tensor");
+    const bool direct = w == kHere;
     float *dst = (float *)user;
     if (!direct) {
         xnor_nn_status_t st = ensure_stage(x, 2, dst_elems(*p) * sizeof(float));
@@ -362,7 +441,9 @@ xnor_nn_status_t xnor_nn_b200_init_convolution(xnor_nn_convolution_t *c,
 
 xnor_nn_b200_kernel_t xnor_nn_b200_kernel_of(const xnor_nn_convolution_t *c) {
     const Plan *p = plan_of(c);
-    return p ? (xnor_nn_b200_kernel_t)(int)p->family : xnor_nn_b200_kernel_auto;
+    if (!p) return xnor_nn_b200_kernel_auto;
+    if (p->family == kTcgen05 && p->img) return xnor_nn_b200_kernel_tcgen05_i8_rows;
+    return (xnor_nn_b200_kernel_t)(int)p->family;
 }
 
 void xnor_nn_destroy_convolution(xnor_nn_convolution_t *c) {
@@ -391,6 +472,8 @@ void xnor_nn_free_resources(xnor_nn_resources_t res) {
             if (x->stage[i]) cudaFree(x->stage[i]);
         if (x->sums_stage) cudaFree(x->sums_stage);
         if (x->error_word) cudaFree(x->error_word);
+        if (x->error_host) cudaFreeHost(x->error_host);
+        free_shards(x);
         if (x->ev_chain) cudaEventDestroy(x->ev_chain);
         if (x->copy_in) cudaStreamDestroy(x->copy_in);
         if (x->copy_out) cudaStreamDestroy(x->copy_out);
@@ -424,9 +507,12 @@ xnor_nn_status_t xnor_nn_allocate_resources(const xnor_nn_convolution_t *c,
     }
     if (e == cudaSuccess) e = cudaMalloc(&x->error_word, sizeof(int));
     if (e == cudaSuccess) e = cudaMemsetAsync(x->error_word, 0, sizeof(int), x->stream);
+    if (e == cudaSuccess) e = cudaMallocHost(&x->error_host, sizeof(int));
+    if (e == cudaSuccess) *x->error_host = 0;
     if (e == cudaSuccess) e = cudaStreamSynchronize(x->stream);
     if (e != cudaSuccess) {
         if (x->error_word) cudaFree(x->error_word);
+        if (x->error_host) cudaFreeHost(x->error_host);
         for (int i = xnor_nn_resource_internal; i < xnor_nn_resource_number; i++) {
             if (res[i]) cudaFree(res[i]);
             res[i] = nullptr;
@@ -486,6 +572,7 @@ Slice slice_of(const Plan &p, int first, int count) {
     s.p.mb = count;
     s.p.q_total = (long)count * p.hp * p.wp;
     s.p.rows = p.lead + s.p.q_total + 256 + (long)p.kh * p.wp + p.kw;
+    if (count != p.mb) plan_image_rows(&s.p);  // the tiling depends on the image count
     s.src = (size_t)first * p.ic * p.ih * p.iw * sizeof(float);
     s.a = (size_t)first * p.ih * p.iw * sizeof(float);
     s.k = (size_t)first * p.oh * p.ow * sizeof(float);
@@ -515,8 +602,10 @@ xnor_nn_status_t enqueue_forward(const Slice &sl, ResCtx *x, xnor_nn_resources_t
 
 // Host source and host result: the minibatch is cut into slices whose upload, kernels and
 // download overlap (PCIe is full duplex and both copy engines run beside the SMs), so the call
-// costs about the longer of the two transfers instead of their sum plus the kernels.
-xnor_nn_status_t forward_host_pipelined(const Plan &p, ResCtx *x, xnor_nn_resources_t res) {
+// costs about the longer of the two transfers instead of their sum plus the kernels. A slice
+// carries at least kSliceBytes of source: below that the per-slice event hops cost more than the
+// overlap gains. Everything is only enqueued; the caller synchronises.
+xnor_nn_status_t enqueue_host_pipelined(const Plan &p, ResCtx *x, xnor_nn_resources_t res) {
     const char *h_src = (const char *)res[xnor_nn_resource_user_src];
     char *h_dst = (char *)res[xnor_nn_resource_user_dst];
     xnor_nn_status_t st = ensure_stage(x, 0, src_bytes(p));
@@ -531,8 +620,9 @@ xnor_nn_status_t forward_host_pipelined(const Plan &p, ResCtx *x, xnor_nn_resour
         }
         CU(cudaEventCreateWithFlags(&x->ev_edge, cudaEventDisableTiming));
     }
-    int slices = p.mb / 8;
+    long slices = (long)(src_bytes(p) / ResCtx::kSliceBytes);
     if (slices > ResCtx::kMaxSlices) slices = ResCtx::kMaxSlices;
+    if (slices > p.mb) slices = p.mb;
     if (slices < 1) slices = 1;
     // the copy streams start after whatever the caller already queued on the main stream
     CU(cudaEventRecord(x->ev_edge, x->stream));
@@ -557,7 +647,25 @@ xnor_nn_status_t forward_host_pipelined(const Plan &p, ResCtx *x, xnor_nn_resour
     }
     CU(cudaEventRecord(x->ev_edge, x->copy_out));
     CU(cudaStreamWaitEvent(x->stream, x->ev_edge, 0));
-    return sync_and_check(x);
+    return xnor_nn_success;
+}
+
+xnor_nn_status_t forward_host_pipelined(const Plan &p, ResCtx *x, xnor_nn_resources_t res) {
+    const xnor_nn_status_t st = enqueue_host_pipelined(p, x, res);
+    return st == xnor_nn_success ? sync_and_check(x) : st;
+}
+
+void free_shards(ResCtx *x) {
+    for (int i = 0; i < x->n_shards; i++) {
+        ResCtx::Shard &sh = x->shards[i];
+        if (!sh.c.state) continue;
+        DeviceGuard dg(sh.device);
+        xnor_nn_free_resources(sh.res);
+        xnor_nn_destroy_convolution(&sh.c);
+    }
+    delete[] x->shards;
+    x->shards = nullptr;
+    x->n_shards = 0;
 }
 
 }  // namespace
@@ -577,8 +685,12 @@ xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_re
     if (!p->formats_ok) return xnor_nn_unimplemented;
     DeviceGuard dg(x->device);
     log_exec(*p, "fused forward");
-    if (p->mb >= 16 && !on_device(res[xnor_nn_resource_user_src]) &&
-        !on_device(res[xnor_nn_resource_user_dst]))
+    x->staged_a_valid = false;
+    const Where ws = where_is(res[xnor_nn_resource_user_src], x->device);
+    const Where wd = where_is(res[xnor_nn_resource_user_dst], x->device);
+    if (ws == kElsewhere) return wrong_device("the source tensor");
+    if (wd == kElsewhere) return wrong_device("the result tensor");
+    if (ws == kHost && wd == kHost && src_bytes(*p) >= 2 * ResCtx::kSliceBytes)
         return forward_host_pipelined(*p, x, res);
     const void *src = nullptr;
     bool staged = false;
@@ -768,6 +880,135 @@ xnor_nn_status_t xnor_nn_b200_binarize_weights_float(const xnor_nn_convolution_t
 }
 
 long xnor_nn_b200_kernel_launches(void) { return g_kernel_launches.load(); }
+
+xnor_nn_status_t xnor_nn_b200_forward_sharded(const xnor_nn_convolution_t *c,
+                                              xnor_nn_resources_t res, const int *devices,
+                                              int n_devices) {
+    if (!c || !res) return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x) return xnor_nn_error_invalid_input;
+    if (n_devices == 0) {  // drop the replicas
+        free_shards(x);
+        return xnor_nn_success;
+    }
+    if (!devices || n_devices < 0 || n_devices > 64 || !res[xnor_nn_resource_user_src] ||
+        !res[xnor_nn_resource_user_dst])
+        return xnor_nn_error_invalid_input;
+    if (!p->formats_ok) return xnor_nn_unimplemented;
+    int present = 0;
+    CU(cudaGetDeviceCount(&present));
+    for (int i = 0; i < n_devices; i++) {
+        if (devices[i] < 0 || devices[i] >= present) {
+            snprintf(t_last_error, sizeof t_last_error,
+                     "device %d was asked for, %d are present", devices[i], present);
+            return xnor_nn_error_invalid_input;
+        }
+        for (int j = 0; j < i; j++)
+            if (devices[j] == devices[i]) return xnor_nn_error_invalid_input;
+    }
+    if (on_device(res[xnor_nn_resource_user_src]) || on_device(res[xnor_nn_resource_user_dst])) {
+        snprintf(t_last_error, sizeof t_last_error,
+                 "the sharded call takes the minibatch from, and gathers it into, host memory");
+        return xnor_nn_error_invalid_input;
+    }
+    // (Re)build the per-device replicas: on first use, when the device list changes, and when
+    // the caller has put a weights tensor into res[user_weights] again.
+    bool rebuild = x->n_shards != n_devices || res[xnor_nn_resource_user_weights] != nullptr;
+    for (int i = 0; !rebuild && i < n_devices; i++) rebuild = x->shards[i].device != devices[i];
+    if (rebuild) {
+        if (!res[xnor_nn_resource_user_weights]) {
+            snprintf(t_last_error, sizeof t_last_error,
+                     "res[user_weights] must hold the weights when the device list is new");
+            return xnor_nn_error_invalid_input;
+        }
+        free_shards(x);
+        x->shards = new (std::nothrow) ResCtx::Shard[n_devices];
+        if (!x->shards) return xnor_nn_error_memory;
+        x->n_shards = n_devices;
+        for (int i = 0; i < n_devices; i++) {
+            ResCtx::Shard &sh = x->shards[i];
+            sh.device = devices[i];
+            // contiguous image slices in minibatch order, as upstream's outermost loop walks
+            // them (src/default/bcast_convolution_default.cpp:60-64)
+            sh.first = (int)((long)p->mb * i / n_devices);
+            sh.count = (int)((long)p->mb * (i + 1) / n_devices) - sh.first;
+            if (sh.count == 0) continue;
+            DeviceGuard dg(sh.device);
+            xnor_nn_status_t st = init_common(
+                &sh.c, c->algorithm, c->src_format, c->weights_format, c->dst_format, sh.count,
+                c->oc, c->ic, c->ih, c->iw, c->kh, c->kw, c->sh, c->sw, c->ph, c->pw,
+                p->family == kTcgen05 && p->img ? kTcgen05Rows : p->family);
+            if (st == xnor_nn_success) st = xnor_nn_allocate_resources(&sh.c, sh.res);
+            if (st == xnor_nn_success) {
+                sh.res[xnor_nn_resource_user_weights] = res[xnor_nn_resource_user_weights];
+                st = exec_binarize_weights(&sh.c, sh.res);
+                sh.res[xnor_nn_resource_user_weights] = nullptr;
+            }
+            if (st != xnor_nn_success) {
+                free_shards(x);
+                return st;
+            }
+        }
+    }
+    // Enqueue every device's slice (upload, kernels, download on that device's streams), then
+    // wait for all of them: no peer access, no collective, the gather is the downloads landing
+    // in the caller's one result tensor.
+    const size_t src_img = (size_t)p->ic * p->ih * p->iw * sizeof(float);
+    const size_t dst_img = (size_t)p->oc * p->oh * p->ow * sizeof(float);
+    xnor_nn_status_t status = xnor_nn_success;
+    for (int i = 0; i < n_devices && status == xnor_nn_success; i++) {
+        ResCtx::Shard &sh = x->shards[i];
+        if (sh.count == 0) continue;
+        DeviceGuard dg(sh.device);
+        sh.res[xnor_nn_resource_user_src] =
+            (char *)res[xnor_nn_resource_user_src] + (size_t)sh.first * src_img;
+        sh.res[xnor_nn_resource_user_dst] =
+            (char *)res[xnor_nn_resource_user_dst] + (size_t)sh.first * dst_img;
+        status = enqueue_host_pipelined(*plan_of(&sh.c), find_ctx(sh.res), sh.res);
+    }
+    for (int i = 0; i < n_devices; i++) {
+        ResCtx::Shard &sh = x->shards[i];
+        if (sh.count == 0) continue;
+        DeviceGuard dg(sh.device);
+        const xnor_nn_status_t st = sync_and_check(find_ctx(sh.res));
+        if (status == xnor_nn_success) status = st;
+        sh.res[xnor_nn_resource_user_src] = nullptr;
+        sh.res[xnor_nn_resource_user_dst] = nullptr;
+    }
+    return status;
+}
+
+xnor_nn_status_t xnor_nn_b200_selftest_lost_commit(const xnor_nn_convolution_t *c,
+                                                   xnor_nn_resources_t res, unsigned wait_ms) {
+    if (!c || !res || !res[xnor_nn_resource_user_dst] || !res[xnor_nn_resource_bin_src] ||
+        !res[xnor_nn_resource_bin_weights] || !res[xnor_nn_resource_k] ||
+        !res[xnor_nn_resource_alpha])
+        return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x || p->family != kTcgen05 || wait_ms == 0 || wait_ms > 1000 ||
+        where_is(res[xnor_nn_resource_user_dst], x->device) != kHere)
+        return xnor_nn_error_invalid_input;
+    DeviceGuard dg(x->device);
+    ConvSelfTest t;
+    t.wait_ns = (unsigned long long)wait_ms * 1000000ull;
+    t.drop_commit = 1;
+    float *dst = (float *)res[xnor_nn_resource_user_dst];
+    if (p->img)
+        CU(launch_conv_tcgen05_img(*p, res[xnor_nn_resource_bin_src],
+                                   res[xnor_nn_resource_bin_weights],
+                                   (const float *)res[xnor_nn_resource_alpha],
+                                   (const float *)res[xnor_nn_resource_k], nullptr, nullptr, dst,
+                                   nullptr, x->error_word, x->stream, &t));
+    else
+        CU(launch_conv_tcgen05(*p, res[xnor_nn_resource_bin_src],
+                               res[xnor_nn_resource_bin_weights],
+                               (const float *)res[xnor_nn_resource_alpha],
+                               (const float *)res[xnor_nn_resource_k], nullptr, nullptr, dst,
+                               nullptr, x->error_word, x->stream, nullptr, &t));
+    return sync_and_check(x);
+}
 
 }  // extern "C"
 #pragma GCC visibility pop

@@ -22,16 +22,6 @@
 //               order and store; runs under the next tile's MMAs thanks to the second
 //               accumulator
 //
-// Two kernels share these roles. The per-tap kernel loads an A tile and a weight tile per
-// pipeline stage (one filter tap x one channel chunk). The slab kernel uses that the KH*KW
-// shifted A tiles of a position tile overlap almost entirely: it loads their union once per group
-// of channel chunks (128 + (KH-1)*(IW+PW) + KW-1 rows, a "slab") and points each tap's matrix
-// descriptor at a row offset inside it (the swizzle is a function of the absolute shared-memory
-// address, so a descriptor may start at any row); only the weights are streamed per tap, several
-// chunks per stage. The launcher picks the slab kernel where that packs more MMAs into a stage
-// (narrow chunks: the 5x5 layer with 96 channels) and the per-tap kernel elsewhere, where the two
-// are within a few percent of each other.
-//
 // The epilogue has three forms: floats in NCHW (a warp store is one contiguous run of a filter
 // plane), floats in NHWC (a thread owns whole 32-byte sectors and writes them with 256-bit
 // stores), and, for chained layers, no floats at all: the sign byte of every result goes into the
@@ -41,20 +31,23 @@
 // in *error, every role winds down, copies in flight are waited for (again bounded), tensor
 // memory is released and the kernel returns.
 #include <cuda.h>
-#include <cstdlib>
+
+#include <atomic>
 
 #include "kernels.cuh"
+#include "tc_ptx.cuh"
 
 namespace xb200 {
 
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128;            // positions per tile = UMMA M = TMEM lanes
 constexpr int kStages = 4;
 constexpr int kEpiWarps = 16;       // epilogue warps: 4 TMEM lane quadrants x column groups
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct TcArgs {
     const float *alpha;
@@ -74,136 +67,24 @@ struct TcArgs {
     uint32_t desc_hi;  // upper 32 bits of the shared-memory matrix descriptors
     uint32_t a_bytes, stage_bytes, tx_bytes;
     int dst_nhwc;
-    // slab kernel only
-    int group;            // channel chunks per weight stage (G)
-    int groups_per_tile;  // chunks_per_tap / G
-    int slab_rows;        // rows of a slab, multiple of 8, <= 256
-    int n_slabs;          // slab-ring depth, counted in groups
-    int n_ring;           // weight-ring depth
-    uint32_t slab_chunk_bytes, slab_group_bytes, b_chunk_bytes, b_stage_bytes;
-    uint32_t slab_tx_bytes, b_tx_bytes;  // bytes TMA writes per group / stage (the boxes)
     // chained layers: instead of floats the epilogue writes the next layer's packed input
     uint8_t *emit_bin;    // next layer's +-1 byte frame, or null
     float *emit_a;        // next layer's mean-|x| map
     int e_wp, e_hp, e_lead, e_icp;  // the next layer's frame geometry
     float e_inv_ic;       // 1.f / (next layer's channels = this layer's filters)
     int n_inner;          // 1: a CTA works through all filter tiles of a pixel tile in a row
+    unsigned long long wait_ns;  // bound of every mbarrier wait
+    int drop_commit;      // self-test: CTA 0 leaves out the commit that publishes its first tile
 };
-
-// ---- PTX wrappers ------------------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Waits for a barrier phase, giving up after kWaitLimitNs or as soon as another role has given
-// up. Returns false in that case, after recording `code` (first failure wins).
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                       int *error, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-        for (int i = 0; i < 64; i++)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (global_ns() - t0 > kWaitLimitNs) {
-            *abort_flag = 1;
-            atomicCAS(error, 0, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// Arrives on the barrier once every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t *v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-          "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr));
-}
-
-__device__ __forceinline__ void tc_wait_ld() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 // ---- the kernel --------------------------------------------------------------------------------
 
 constexpr int kAlphaSmem = 2048;  // filters whose alpha is staged in shared memory
 
-constexpr int kMaxRing = 8;   // weight-ring depth limit of the slab kernel
-constexpr int kMaxSlabs = 8;  // slab-ring depth limit
 
 struct __align__(16) Control {
-    unsigned long long full[kMaxRing];
-    unsigned long long empty[kMaxRing];
-    unsigned long long slab_full[kMaxSlabs];
-    unsigned long long slab_empty[kMaxSlabs];
+    unsigned long long full[kStages];
+    unsigned long long empty[kStages];
     unsigned long long acc_full[2];
     unsigned long long acc_empty[2];
     unsigned long long drain;
@@ -213,19 +94,6 @@ struct __align__(16) Control {
     float fold[2][4][kEpiWarps / 4][32];  // chained layers: per-warp partial sums of |y|
 };
 constexpr int kControlBytes = (sizeof(Control) + 1023) / 1024 * 1024;
-
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr));
-}
 
 // Which tile a CTA works on in its it-th round. Default: tiles are dealt round-robin with the
 // filter tile as the fast index. n_inner: pixel tiles are dealt round-robin and a CTA walks all
@@ -251,7 +119,7 @@ __device__ __forceinline__ void tile_at(const TcArgs &g, int it, int &mt, int &n
     }
 }
 
-// ---- epilogue role (both kernels) ----------------------------------------------------------------
+// ---- epilogue role ---------------------------------------------------------------------------------
 // Warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); several warps share a quadrant and split
 // its columns between them.
 __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uint32_t tmem_base,
@@ -263,9 +131,9 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
     const int cgroup = (warp - 2) >> 2, cgroups = kEpiWarps / 4;
     const int frame = g.hp * g.wp;
     const long ohw = (long)g.oh * g.ow;
-    bool ok = true;
+    bool ok = true;   // false once a wait ran out somewhere in the CTA
     float run = 0.f;  // chained layers: running sum of |y| over the filter tiles of a pixel
-    for (int it = 0; ok && it < rounds; it++) {
+    for (int it = 0; it < rounds; it++) {
         int mt, nt;
         tile_at(g, it, mt, nt);
         const int b = it & 1;
@@ -299,10 +167,19 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
         }
         const int oc0 = nt * g.n_tile;
         const int n_valid = min(g.n_tile, g.oc - oc0);  // real filters in this tile
-        ok = mbar_wait(smem_u32(&ctl->acc_full[b]), acc_phase, abort_flag, g.error, 4);
+        if (ok)
+            ok = mbar_wait(smem_u32(&ctl->acc_full[b]), acc_phase, abort_flag, g.error, 4,
+                           g.wait_ns);
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
-        if (!ok) break;
-        tc_fence_after();
+        if (!ok) {
+            // Given up: touch nothing any more. The chained epilogue's warps of a quadrant meet
+            // on a named barrier once per tile; a warp that has given up keeps that appointment
+            // so that one that has not (yet) cannot be left waiting there.
+            if (!g.emit_bin) break;
+            bar_sync(1 + quad, 32 * (kEpiWarps / 4));
+            continue;
+        }
+        fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
         if (g.emit_bin) {
             // Chained layers: y = (S * alpha) * K is not stored. alpha and K are never negative,
@@ -319,13 +196,13 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
                 uint32_t v[32];
                 const int width = g.n_tile - c0 >= 32 ? 32 : 16;
                 if (width == 32) {
-                    tc_ld32(taddr + (uint32_t)c0, v);
+                    ld32(taddr + (uint32_t)c0, v);
                 } else {
 #pragma unroll
                     for (int j = 16; j < 32; j++) v[j] = 0;
-                    tc_ld16(taddr + (uint32_t)c0, v);
+                    ld16(taddr + (uint32_t)c0, v);
                 }
-                tc_wait_ld();
+                wait_ld();
                 if (valid) {
                     const int lim = min(n_valid - c0, width);
                     uint32_t w[8];
@@ -377,7 +254,7 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
             // next filter tile), so the map is reproducible; the four warps of a lane quadrant
             // meet on a named barrier of their own.
             ctl->fold[it & 1][quad][cgroup][lane] = part;
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + quad), "r"(32 * (kEpiWarps / 4)) : "memory");
+            bar_sync(1 + quad, 32 * (kEpiWarps / 4));
             if (cgroup == 0) {
                 if (nt == 0) run = 0.f;
 #pragma unroll
@@ -394,11 +271,11 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
             for (int c0 = 32 * cgroup; c0 < g.n_tile; c0 += 32 * cgroups) {
                 uint32_t v[32];
                 if (c0 + 32 <= g.n_tile) {
-                    tc_ld32(taddr + (uint32_t)c0, v);
+                    ld32(taddr + (uint32_t)c0, v);
                 } else {  // N is a multiple of 16, not always of 32
-                    tc_ld16(taddr + (uint32_t)c0, v);
+                    ld16(taddr + (uint32_t)c0, v);
                 }
-                tc_wait_ld();
+                wait_ld();
                 if (valid) {
                     const int lim = n_valid - c0;
                     float *o = out + (long)c0 * ohw;
@@ -433,8 +310,8 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
             const bool wide = (g.oc & 7) == 0 && (oc0 & 7) == 0 && ((uintptr_t)g.dst & 31) == 0;
             for (int c0 = 16 * cgroup; c0 < g.n_tile; c0 += 16 * cgroups) {
                 uint32_t v[16];
-                tc_ld16(taddr + (uint32_t)c0, v);
-                tc_wait_ld();
+                ld16(taddr + (uint32_t)c0, v);
+                wait_ld();
                 if (valid && wide && c0 + 16 <= n_valid) {
                     // 16 results = two whole 32-byte sectors, one 256-bit store each
                     float x[16];
@@ -464,8 +341,8 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
         } else {
             for (int c0 = 16 * cgroup; c0 < g.n_tile; c0 += 16 * cgroups) {
                 uint32_t v[16];
-                tc_ld16(taddr + (uint32_t)c0, v);
-                tc_wait_ld();
+                ld16(taddr + (uint32_t)c0, v);
+                wait_ld();
                 if (valid) {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
@@ -483,7 +360,7 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
                 }
             }
         }
-        tc_fence_before();
+        fence_before();
         mbar_arrive(smem_u32(&ctl->acc_empty[b]));
     }
 }
@@ -519,19 +396,16 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
     }
     // Everything above touched only this CTA's own shared and tensor memory and the launch
     // parameters. What earlier kernels of the stream produced is read by the TMA producer and
     // the epilogue warps, each after its own dependency_wait(); the MMA issuer reads shared
     // memory only.
     const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
-    tc_fence_before();
+    fence_before();
     __syncthreads();
-    tc_fence_after();
+    fence_after();
     // Every CTA of this grid is resident from the start, so a dependent grid may be launched as
     // soon as all of them have got here: its CTAs move in as these exit (SMs with one tile fewer
     // exit a round early) and set themselves up; they wait for this grid's results themselves.
@@ -560,7 +434,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 for (int ks = 0; ks < ksteps; ks++) {
                     const uint32_t ebar = smem_u32(&ctl->empty[stage]);
                     if (!mbar_try_wait(ebar, phase ^ 1)) {
-                        ok = mbar_wait(ebar, phase ^ 1, abort_flag, g.error, 1);
+                        ok = mbar_wait(ebar, phase ^ 1, abort_flag, g.error, 1, g.wait_ns);
                         if (!ok) break;
                     }
                     armed &= ~(1u << stage);
@@ -585,10 +459,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 // memory: wait for them (bounded) before the CTA may exit.
                 for (int s = 0; s < kStages; s++)
                     if (armed & (1u << s)) {
-                        const uint32_t bar = smem_u32(&ctl->full[s]);
-                        const unsigned long long t0 = global_ns();
-                        while (!mbar_try_wait(bar, (armed_parity >> s) & 1u))
-                            if (global_ns() - t0 > kWaitLimitNs) break;
+                        mbar_wait_quiet(smem_u32(&ctl->full[s]), (armed_parity >> s) & 1u,
+                                        g.wait_ns);
                     }
             }
         }
@@ -605,37 +477,36 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             for (int it = 0; ok && it < rounds; it++) {
                 const int b = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
-                ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2);
+                ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2, g.wait_ns);
                 if (!ok) break;
-                tc_fence_after();
+                fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
                 uint32_t accumulate = 0;
                 for (int ks = 0; ks < ksteps; ks++) {
                     const uint32_t fbar = smem_u32(&ctl->full[stage]);
                     if (!mbar_try_wait(fbar, phase)) {
-                        ok = mbar_wait(fbar, phase, abort_flag, g.error, 3);
+                        ok = mbar_wait(fbar, phase, abort_flag, g.error, 3, g.wait_ns);
                         if (!ok) break;
                     }
-                    tc_fence_after();
+                    fence_after();
                     const uint64_t adesc = hi | (uint64_t)(a_lo0 + (uint32_t)stage * stage_units);
                     const uint64_t bdesc = hi | (uint64_t)(b_lo0 + (uint32_t)stage * stage_units);
 #pragma unroll
                     for (int k = 0; k < KK; k++) {
-                        tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
+                        mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
                                   g.idesc, k == 0 ? accumulate : 1u);
                     }
                     accumulate = 1;
-                    tc_commit(smem_u32(&ctl->empty[stage]));
+                    commit(smem_u32(&ctl->empty[stage]));
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
-                if (ok) tc_commit(smem_u32(&ctl->acc_full[b]));
+                if (ok && !(g.drop_commit && it == 0 && blockIdx.x == 0))
+                    commit(smem_u32(&ctl->acc_full[b]));
             }
             if (!ok) {
                 // Let every MMA already issued finish before tensor memory is released.
-                tc_commit(smem_u32(&ctl->drain));
-                const unsigned long long t0 = global_ns();
-                while (!mbar_try_wait(smem_u32(&ctl->drain), 0))
-                    if (global_ns() - t0 > kWaitLimitNs) break;
+                commit(smem_u32(&ctl->drain));
+                mbar_wait_quiet(smem_u32(&ctl->drain), 0, g.wait_ns);
             }
         }
         __syncwarp();
@@ -645,314 +516,27 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (alpha_in_smem) {
             for (int i = threadIdx.x - 64; i < g.ocp16; i += 32 * kEpiWarps)
                 ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
-            asm volatile("bar.sync %0, %1;" ::"r"(5), "r"(32 * kEpiWarps) : "memory");
+            bar_sync(5, 32 * kEpiWarps);
         }
         epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
-    tc_fence_before();
+    fence_before();
     __syncthreads();
     if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"(kTmemCols)
-                     : "memory");
-    }
-}
-
-// ---- slab kernel -------------------------------------------------------------------------------
-//
-// K order of a tile: channel-chunk group (outer) x filter tap (inner). A group is G consecutive
-// chunks of kchunk channels; its slab (G buffers of slab_rows x kchunk bytes) stays resident
-// for all taps while the weight ring streams one stage per tap (G boxes of n_tile x kchunk
-// bytes). A stage therefore feeds G*KK tcgen05.mma instructions.
-template <int KK>
-__global__ void __launch_bounds__(kThreads, 1)
-conv_tcgen05_slab_kernel(const __grid_constant__ CUtensorMap map_a,
-                         const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    Control *ctl = (Control *)base;
-    const uint32_t slab0 = smem_u32(base + kControlBytes);
-    const uint32_t ring0 = slab0 + (uint32_t)g.n_slabs * g.slab_group_bytes;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    volatile int *abort_flag = &ctl->abort_flag;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kMaxRing; s++) {
-            mbar_init(smem_u32(&ctl->full[s]), 1);
-            mbar_init(smem_u32(&ctl->empty[s]), 1);
-        }
-        for (int s = 0; s < kMaxSlabs; s++) {
-            mbar_init(smem_u32(&ctl->slab_full[s]), 1);
-            mbar_init(smem_u32(&ctl->slab_empty[s]), 1);
-        }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(smem_u32(&ctl->acc_full[b]), 1);
-            mbar_init(smem_u32(&ctl->acc_empty[b]), 32 * kEpiWarps);
-        }
-        mbar_init(smem_u32(&ctl->drain), 1);
-        ctl->abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // the descriptors are launch parameters: fetch them while the predecessor still runs
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    // Everything above touched only this CTA's own shared and tensor memory and the launch
-    // parameters. What earlier kernels of the stream produced is read by the TMA producer and
-    // the epilogue warps, each after its own dependency_wait(); the MMA issuer reads shared
-    // memory only.
-    const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    // Every CTA of this grid is resident from the start, so a dependent grid may be launched as
-    // soon as all of them have got here: its CTAs move in as these exit (SMs with one tile fewer
-    // exit a round early) and set themselves up; they wait for this grid's results themselves.
-    dependency_release();
-    const uint32_t tmem_base = ctl->tmem_base;
-    const int rounds = tile_rounds(g);
-
-    if (warp == 0) {
-        if (lane == 0) {
-            // ---- TMA producer ----
-            dependency_wait();
-            int stage = 0, slab = 0;
-            uint32_t phase = 0, slab_phase = 0;
-            uint32_t armed = 0, armed_parity = 0;            // weight ring
-            uint32_t slab_armed = 0, slab_armed_parity = 0;  // slab ring
-            bool ok = true;
-            for (int it = 0; ok && it < rounds; it++) {
-                int mt, nt;
-                tile_at(g, it, mt, nt);
-                const int row0 = g.lead + mt * BM - g.ph * g.wp - g.pw;  // first slab row
-                for (int cg = 0; ok && cg < g.groups_per_tile; cg++) {
-                    // the slab of this chunk group
-                    {
-                        const uint32_t ebar = smem_u32(&ctl->slab_empty[slab]);
-                        if (!mbar_try_wait(ebar, slab_phase ^ 1)) {
-                            ok = mbar_wait(ebar, slab_phase ^ 1, abort_flag, g.error, 5);
-                            if (!ok) break;
-                        }
-                        slab_armed &= ~(1u << slab);
-                        const uint32_t bar = smem_u32(&ctl->slab_full[slab]);
-                        const uint32_t dst = slab0 + (uint32_t)slab * g.slab_group_bytes;
-                        mbar_expect_tx(bar, g.slab_tx_bytes);
-                        for (int c = 0; c < g.group; c++)
-                            tma_load_2d(dst + (uint32_t)c * g.slab_chunk_bytes, &map_a,
-                                        (cg * g.group + c) * g.kchunk, row0, bar);
-                        slab_armed |= 1u << slab;
-                        slab_armed_parity =
-                            (slab_armed_parity & ~(1u << slab)) | (slab_phase << slab);
-                        if (++slab == g.n_slabs) { slab = 0; slab_phase ^= 1; }
-                    }
-                    // one weight stage per tap
-                    int brow = nt * g.n_tile;
-                    for (int t = 0; t < g.taps; t++, brow += g.ocp16) {
-                        const uint32_t ebar = smem_u32(&ctl->empty[stage]);
-                        if (!mbar_try_wait(ebar, phase ^ 1)) {
-                            ok = mbar_wait(ebar, phase ^ 1, abort_flag, g.error, 1);
-                            if (!ok) break;
-                        }
-                        armed &= ~(1u << stage);
-                        const uint32_t bar = smem_u32(&ctl->full[stage]);
-                        const uint32_t dst = ring0 + (uint32_t)stage * g.b_stage_bytes;
-                        mbar_expect_tx(bar, g.b_tx_bytes);
-                        for (int c = 0; c < g.group; c++)
-                            tma_load_2d(dst + (uint32_t)c * g.b_chunk_bytes, &map_b,
-                                        (cg * g.group + c) * g.kchunk, brow, bar);
-                        armed |= 1u << stage;
-                        armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-                        if (++stage == g.n_ring) { stage = 0; phase ^= 1; }
-                    }
-                }
-            }
-            if (!ok) {
-                // Loads already issued still land in this CTA's shared memory: wait for them
-                // (bounded) before the CTA may exit.
-                for (int s = 0; s < kMaxRing; s++)
-                    if (armed & (1u << s)) {
-                        const unsigned long long t0 = global_ns();
-                        while (!mbar_try_wait(smem_u32(&ctl->full[s]), (armed_parity >> s) & 1u))
-                            if (global_ns() - t0 > kWaitLimitNs) break;
-                    }
-                for (int s = 0; s < kMaxSlabs; s++)
-                    if (slab_armed & (1u << s)) {
-                        const unsigned long long t0 = global_ns();
-                        while (!mbar_try_wait(smem_u32(&ctl->slab_full[s]),
-                                              (slab_armed_parity >> s) & 1u))
-                            if (global_ns() - t0 > kWaitLimitNs) break;
-                    }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- MMA issuer ----
-            int stage = 0, slab = 0;
-            uint32_t phase = 0, slab_phase = 0;
-            bool ok = true;
-            const uint64_t hi = (uint64_t)g.desc_hi << 32;
-            const uint32_t a_lo0 = ((slab0 >> 4) & 0x3FFF) | (1u << 16);
-            const uint32_t b_lo0 = ((ring0 >> 4) & 0x3FFF) | (1u << 16);
-            const uint32_t row_units = (uint32_t)g.kchunk >> 4;  // one slab row, 16-byte units
-            for (int it = 0; ok && it < rounds; it++) {
-                const int b = it & 1;
-                const uint32_t acc_phase = (it >> 1) & 1;
-                ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
-                uint32_t accumulate = 0;
-                for (int cg = 0; ok && cg < g.groups_per_tile; cg++) {
-                    const uint32_t sbar = smem_u32(&ctl->slab_full[slab]);
-                    if (!mbar_try_wait(sbar, slab_phase)) {
-                        ok = mbar_wait(sbar, slab_phase, abort_flag, g.error, 6);
-                        if (!ok) break;
-                    }
-                    const uint32_t a_slab = a_lo0 + (uint32_t)slab * (g.slab_group_bytes >> 4);
-                    uint32_t a_tap = a_slab;  // descriptor of tap (0,0): slab row 0
-                    int kw = 0;
-                    for (int t = 0; t < g.taps; t++) {
-                        const uint32_t fbar = smem_u32(&ctl->full[stage]);
-                        if (!mbar_try_wait(fbar, phase)) {
-                            ok = mbar_wait(fbar, phase, abort_flag, g.error, 3);
-                            if (!ok) break;
-                        }
-                        tc_fence_after();
-                        const uint32_t b_lo = b_lo0 + (uint32_t)stage * (g.b_stage_bytes >> 4);
-                        for (int c = 0; c < g.group; c++) {
-                            const uint64_t adesc = hi | (uint64_t)(a_tap + (uint32_t)c * (g.slab_chunk_bytes >> 4));
-                            const uint64_t bdesc = hi | (uint64_t)(b_lo + (uint32_t)c * (g.b_chunk_bytes >> 4));
-#pragma unroll
-                            for (int k = 0; k < KK; k++) {
-                                tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k),
-                                          bdesc + (uint64_t)(2 * k), g.idesc,
-                                          (k == 0 && c == 0) ? accumulate : 1u);
-                            }
-                        }
-                        accumulate = 1;
-                        tc_commit(smem_u32(&ctl->empty[stage]));
-                        if (++stage == g.n_ring) { stage = 0; phase ^= 1; }
-                        // next tap: one position to the right, or down to the next frame row
-                        if (++kw == g.kw) { kw = 0; a_tap += (uint32_t)(g.wp - (g.kw - 1)) * row_units; }
-                        else a_tap += row_units;
-                    }
-                    if (ok) tc_commit(smem_u32(&ctl->slab_empty[slab]));
-                    if (++slab == g.n_slabs) { slab = 0; slab_phase ^= 1; }
-                }
-                if (ok) tc_commit(smem_u32(&ctl->acc_full[b]));
-            }
-            if (!ok) {
-                // Let every MMA already issued finish before tensor memory is released.
-                tc_commit(smem_u32(&ctl->drain));
-                const unsigned long long t0 = global_ns();
-                while (!mbar_try_wait(smem_u32(&ctl->drain), 0))
-                    if (global_ns() - t0 > kWaitLimitNs) break;
-            }
-        }
-        __syncwarp();
-    } else {
-        // ---- epilogue warps: stage alpha among themselves, then drain accumulators ----
-        dependency_wait();
-        if (alpha_in_smem) {
-            for (int i = threadIdx.x - 64; i < g.ocp16; i += 32 * kEpiWarps)
-                ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
-            asm volatile("bar.sync %0, %1;" ::"r"(5), "r"(32 * kEpiWarps) : "memory");
-        }
-        epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"(kTmemCols)
-                     : "memory");
+        fence_after();
+        tmem_free(tmem_base, kTmemCols);
     }
 }
 
 // ---- host side ---------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
-                cudaSuccess || q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return (EncodeTiledFn)p;
-    }();
-    return fn;
-}
-
-bool encode_bytes_2d_uncached(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes,
-                              uint32_t box_bytes, uint32_t box_rows);
-
-// A [rows][row_bytes] byte matrix, boxes of box_rows x box_bytes, swizzle span = box_bytes.
-// The last few encodings are kept per thread: a layer is launched over and over with the same
-// buffers, and for one-image batches the two driver calls were a visible part of the launch.
-bool encode_bytes_2d(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes,
-                     uint32_t box_bytes, uint32_t box_rows) {
-    struct Entry {
-        const void *ptr;
-        uint64_t rows, row_bytes;
-        uint32_t box_bytes, box_rows;
-        CUtensorMap map;
-    };
-    constexpr int kEntries = 8;
-    thread_local Entry cache[kEntries] = {};
-    thread_local int next = 0;
-    for (int i = 0; i < kEntries; i++) {
-        const Entry &c = cache[i];
-        if (c.ptr == ptr && c.rows == rows && c.row_bytes == row_bytes && c.box_bytes == box_bytes &&
-            c.box_rows == box_rows) {
-            *map = c.map;
-            return true;
-        }
-    }
-    if (!encode_bytes_2d_uncached(map, ptr, rows, row_bytes, box_bytes, box_rows)) return false;
-    Entry &slot = cache[next];
-    next = (next + 1) % kEntries;
-    slot.ptr = ptr; slot.rows = rows; slot.row_bytes = row_bytes;
-    slot.box_bytes = box_bytes; slot.box_rows = box_rows; slot.map = *map;
-    return true;
-}
-
-bool encode_bytes_2d_uncached(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes,
-                              uint32_t box_bytes, uint32_t box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[2] = {row_bytes, rows};
-    const cuuint64_t strides[1] = {row_bytes};
-    const cuuint32_t box[2] = {box_bytes, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapSwizzle sw = box_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
-                                  : box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
-                                                    : CU_TENSOR_MAP_SWIZZLE_32B;
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box,
-              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 }  // namespace
 
 cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *bin_w,
                                 const float *alpha, const float *k, const float *a, float *k_out,
                                 float *dst, int32_t *sums, int *error_word, cudaStream_t s,
-                                const ChainTarget *next) {
+                                const ChainTarget *next, const ConvSelfTest *test) {
     if (p.q_total == 0) return cudaSuccess;
     CUtensorMap map_a, map_b;
     if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk, BM) ||
@@ -973,6 +557,8 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.oh = p.oh; g.ow = p.ow; g.oc = p.oc; g.ocp16 = p.ocp16;
     g.dst_nhwc = p.dst_nhwc;
     g.emit_bin = nullptr; g.emit_a = nullptr; g.n_inner = 0;
+    g.wait_ns = test && test->wait_ns ? test->wait_ns : 2000000000ull;
+    g.drop_commit = test ? test->drop_commit : 0;
     g.e_wp = g.e_hp = g.e_lead = g.e_icp = 0; g.e_inv_ic = 0.f;
     if (next) {
         g.emit_bin = (uint8_t *)next->bin_src; g.emit_a = next->a;
@@ -992,71 +578,31 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.tx_bytes = g.a_bytes + (uint32_t)(p.n_tile * p.kchunk);
     g.stage_bytes = (g.tx_bytes + 1023u) & ~1023u;
 
-    const size_t smem_limit = 227 * 1024;
     const int kk = p.kchunk / 32;
-    // Slab geometry: rows a tile touches over all taps, and how many chunks share a weight stage.
-    const int slab_rows = (BM + (p.kh - 1) * p.wp + (p.kw - 1) + 7) & ~7;
-    int group = 1;
-    for (int cand = g.chunks_per_tap; cand >= 1; cand--)
-        if (g.chunks_per_tap % cand == 0 && cand * kk <= 6) { group = cand; break; }
-    g.group = group;
-    g.groups_per_tile = g.chunks_per_tap / group;
-    g.slab_rows = slab_rows;
-    g.slab_chunk_bytes = (uint32_t)(slab_rows * p.kchunk + 1023) & ~1023u;
-    g.slab_group_bytes = g.slab_chunk_bytes * (uint32_t)group;
-    g.b_chunk_bytes = (uint32_t)(p.n_tile * p.kchunk + 1023) & ~1023u;
-    g.b_stage_bytes = g.b_chunk_bytes * (uint32_t)group;
-    g.slab_tx_bytes = (uint32_t)(group * slab_rows * p.kchunk);
-    g.b_tx_bytes = (uint32_t)(group * p.n_tile * p.kchunk);
-    // Two slab buffers: the next group's slab loads while the current one is in use (a group
-    // lasts KH*KW stages, far longer than a load). The rest of shared memory is weight ring.
-    const size_t fixed = 1024 + kControlBytes;
-    const int n_slabs = 2;
-    long ring = ((long)smem_limit - (long)fixed - (long)n_slabs * g.slab_group_bytes) /
-                (long)g.b_stage_bytes;
-    if (ring > kMaxRing) ring = kMaxRing;
-    g.n_slabs = n_slabs;
-    g.n_ring = (int)ring;
-    // The slab kernel wins where it packs more MMAs into a weight stage than the per-tap kernel
-    // can (measured: 93 vs 131 us on the 5x5 / 96-channel layer); with a single chunk per stage
-    // the per-tap kernel is a little faster (39 vs 43 us on conv4).
-    // XNOR_NN_B200_TCGEN05_VARIANT=slab|pertap overrides the choice (for comparing the two).
-    const char *variant = getenv("XNOR_NN_B200_TCGEN05_VARIANT");
-    const bool use_slab = slab_rows <= 256 && ring >= 3 && (variant ? variant[0] == 's' : group > 1);
-
-    cudaError_t e;
-    size_t smem;
-    void (*kernel)(CUtensorMap, CUtensorMap, TcArgs);
-    if (use_slab) {
-        if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk,
-                             (uint32_t)slab_rows))
-            return cudaErrorNotSupported;
-        smem = fixed + (size_t)n_slabs * g.slab_group_bytes + (size_t)g.n_ring * g.b_stage_bytes;
-        kernel = kk == 4 ? conv_tcgen05_slab_kernel<4>
-                 : kk == 2 ? conv_tcgen05_slab_kernel<2>
-                           : conv_tcgen05_slab_kernel<1>;
-    } else {
-        smem = fixed + (size_t)kStages * g.stage_bytes;
-        kernel = kk == 4 ? conv_tcgen05_kernel<4>
-                 : kk == 2 ? conv_tcgen05_kernel<2>
-                           : conv_tcgen05_kernel<1>;
-    }
+    void (*kernel)(CUtensorMap, CUtensorMap, TcArgs) = kk == 4   ? conv_tcgen05_kernel<4>
+                                                       : kk == 2 ? conv_tcgen05_kernel<2>
+                                                                 : conv_tcgen05_kernel<1>;
+    size_t smem = 1024 + kControlBytes + (size_t)kStages * g.stage_bytes;
     // At least 120 KB of shared memory so that one CTA owns the SM and all 512 TMEM columns.
     if (smem < 120 * 1024) smem = 120 * 1024;
-    // per device, once: the opt-in to large dynamic shared memory and the SM count
+    // per device and kernel, once: the opt-in to large dynamic shared memory and the SM count
     int dev = 0;
     cudaGetDevice(&dev);
-    static int sm_count[64] = {};
-    static bool opted_in[64][6] = {};
-    const int d = dev & 63, v = (use_slab ? 3 : 0) + (kk == 4 ? 0 : kk == 2 ? 1 : 2);
-    if (!opted_in[d][v]) {
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem_limit);
+    static std::atomic<int> sm_count[64];
+    static std::atomic<bool> opted_in[64][3];
+    const int d = dev & 63;
+    std::atomic<bool> &done = opted_in[d][kk == 4 ? 0 : kk == 2 ? 1 : 2];
+    if (!done.load(std::memory_order_acquire)) {
+        const cudaError_t e = cudaFuncSetAttribute(
+            kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
-        opted_in[d][v] = true;
+        done.store(true, std::memory_order_release);
     }
-    if (!sm_count[d]) cudaDeviceGetAttribute(&sm_count[d], cudaDevAttrMultiProcessorCount, dev);
-    const int sms = sm_count[d];
+    int sms = sm_count[d].load(std::memory_order_relaxed);
+    if (!sms) {
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        sm_count[d].store(sms, std::memory_order_relaxed);
+    }
     const int tiles = g.n_inner ? g.m_tiles : g.m_tiles * g.n_tiles;
     const int grid = tiles < sms ? tiles : sms;
     note_launch();

@@ -99,9 +99,25 @@ struct ChainTarget {
     int wp, hp, lead, icp;  // its frame geometry (Plan)
     float inv_ic;         // its Plan::inv_ic
 };
+// `test` (normally null) shortens a tensor-core kernel's wait limit and makes one CTA lose the
+// commit that publishes its first accumulator, so that a test can watch a bounded wait run out:
+// the kernel returns by itself with *error_word set and the results of the call invalid.
+struct ConvSelfTest {
+    unsigned long long wait_ns;  // 0: the normal limit (2 s)
+    int drop_commit;
+};
 cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *bin_w,
                                 const float *alpha, const float *k, const float *a, float *k_out,
                                 float *dst, int32_t *sums, int *error_word, cudaStream_t s,
-                                const ChainTarget *next = nullptr);
+                                const ChainTarget *next = nullptr,
+                                const ConvSelfTest *test = nullptr);
+
+// The same contract (without chaining) with the operand roles swapped: 128 filters on the UMMA M
+// side, whole output rows of one image on the N side (Plan::img_*, conv_tcgen05_img.cu). Reads
+// the same packed operands as launch_conv_tcgen05; the forward pass uses it when Plan::img is set.
+cudaError_t launch_conv_tcgen05_img(const Plan &p, const void *bin_src, const void *bin_w,
+                                    const float *alpha, const float *k, const float *a,
+                                    float *k_out, float *dst, int32_t *sums, int *error_word,
+                                    cudaStream_t s, const ConvSelfTest *test = nullptr);
 
 }  // namespace xb200

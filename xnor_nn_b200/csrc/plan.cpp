@@ -27,8 +27,8 @@ int div_up_i(int a, int b) { return (a + b - 1) / b; }
 const char *family_name(Family f) {
     switch (f) {
         case kPopc: return "popc";
-        case kMmaB1: return "mma_b1";
         case kTcgen05: return "tcgen05_i8";
+        case kTcgen05Rows: return "tcgen05_i8_rows";
         default: return "auto";
     }
 }
@@ -37,19 +37,109 @@ static Family family_from_env() {
     const char *e = getenv("XNOR_NN_B200_KERNEL");
     if (!e) return kAuto;
     if (!strcmp(e, "popc")) return kPopc;
-    if (!strcmp(e, "mma_b1")) return kMmaB1;
     if (!strcmp(e, "tcgen05_i8") || !strcmp(e, "tcgen05")) return kTcgen05;
+    if (!strcmp(e, "tcgen05_i8_rows")) return kTcgen05Rows;
     return kAuto;
 }
 
-// The two tensor-core families walk a zero-framed image with constant row shifts per filter
-// tap, which only describes a unit-stride convolution whose output extent matches the padding
-// actually applied (upstream derives the output height from pw, src/common_convolution.cpp:16).
-static bool frame_walk_ok(const Plan &p) {
-    return p.sh == 1 && p.sw == 1 && p.oh == p.ih + 2 * p.ph - p.kh + 1 &&
-           p.ow == p.iw + 2 * p.pw - p.kw + 1 && p.oh > 0 && p.ow > 0 &&
-           p.kh - 1 - p.ph <= p.ph + p.ih && p.kw - 1 - p.pw <= p.iw &&
+// Both tensor-core kernels read the zero-framed activation bytes and describe a unit-stride
+// convolution only.
+static bool unit_stride(const Plan &p) {
+    return p.sh == 1 && p.sw == 1 && p.oh > 0 && p.ow > 0 &&
            (long)p.mb * (p.ih + p.ph) * (p.iw + p.pw) < (1L << 30);
+}
+
+// The position-tile kernel walks the frame with one constant row shift per filter tap. That
+// needs the output extent to match the padding actually applied (upstream derives the output
+// height from pw, src/common_convolution.cpp:16) and every output pixel to have a frame position
+// of its own, i.e. a padding smaller than the filter (with ph >= kh the output has more rows
+// than the frame).
+static bool frame_walk_ok(const Plan &p) {
+    return unit_stride(p) && p.oh == p.ih + 2 * p.ph - p.kh + 1 &&
+           p.ow == p.iw + 2 * p.pw - p.kw + 1 && p.ph < p.kh && p.pw < p.kw &&
+           p.kh - 1 - p.ph <= p.ph + p.ih && p.kw - 1 - p.pw <= p.iw;
+}
+
+// The image-row kernel addresses the frame as a 4-D tensor (channel, column, row, image) and lets
+// the copy engine fill whatever lies outside with zeros, so any padding and any output extent
+// work; a tile must hold at least one whole output row.
+static bool image_rows_ok(const Plan &p) { return unit_stride(p) && p.ow <= 256; }
+
+// Relative duration of a tile whose UMMA N is n: an instruction occupies the tensor pipe for n/2
+// cycles, but the issuing thread needs about 45 cycles per tcgen05.mma and 275 per
+// tcgen05.commit (measured); with a commit after every four instructions that is 113 cycles per
+// instruction, which is what an N of 226 takes.
+static long tile_cost(int n) { return n < 226 ? 226 : n; }
+
+int img_staging_row_words(const Plan &p) {
+    int w = (p.img_rows * p.ow + 3 + 3) & ~3;
+    if (w % 8 == 0) w += 4;  // an odd multiple of 4: eight rows before a bank repeats
+    return w;
+}
+
+size_t img_staging_bytes(const Plan &p) {
+    size_t words = 32 * (size_t)img_staging_row_words(p);
+    if (p.img_row_blocks == 1 && 32 * (size_t)p.oh * p.ow > words) words = 32 * (size_t)p.oh * p.ow;
+    return (words * 4 + 127) & ~(size_t)127;
+}
+
+void plan_image_rows(Plan *p) {
+    p->img = false;
+    if (p->family != kTcgen05 || !p->img_forced || !image_rows_ok(*p) || p->mb < 1) return;
+    const int sms = sm_count();
+    const int m_blocks = div_up_i(p->oc, 128);
+    long best = -1;
+    int best_r = 0;
+    for (int r = 1; r <= p->oh && r * p->ow <= 256; r++) {
+        const int n = div_up_i(r * p->ow, 16) * 16;
+        const long tiles = (long)p->mb * div_up_i(p->oh, r) * m_blocks;
+        const long rem = tiles % sms;
+        long cost = (tiles / sms) * tile_cost(n);
+        if (rem) {
+            const long half = tile_cost(div_up_i((r + 1) / 2 * p->ow, 16) * 16);
+            const bool split = r >= 2 && 2 * rem <= sms && half < tile_cost(n);
+            cost += split ? half : tile_cost(n);
+        }
+        if (best < 0 || cost <= best) { best = cost; best_r = r; }  // ties: the larger tile
+    }
+    const int r = best_r;
+    p->img_rows = r;
+    p->img_n = div_up_i(r * p->ow, 16) * 16;
+    p->img_row_blocks = div_up_i(p->oh, r);
+    p->img_m_blocks = m_blocks;
+    const long tiles = (long)p->mb * p->img_row_blocks * m_blocks;
+    if (tiles >= (1L << 30)) return;
+    p->img_tiles = (int)tiles;
+    const int rem = (int)(tiles % sms);
+    const bool split = rem && r >= 2 && 2 * rem <= sms &&
+                       tile_cost(div_up_i((r + 1) / 2 * p->ow, 16) * 16) < tile_cost(p->img_n);
+    p->img_whole = split ? (int)tiles - rem : (int)tiles;
+    p->img_half_rows = split ? (r + 1) / 2 : 0;
+    p->img_n_half = split ? div_up_i(p->img_half_rows * p->ow, 16) * 16 : 0;
+    const long units = (long)p->img_whole + 2L * (tiles - p->img_whole);
+    p->img_grid = (int)(units < sms ? units : sms);
+
+    // Shared memory: control block, operand ring, result staging. Two staging buffers let one
+    // pair of epilogue warps fill while the other pair's bulk stores drain; a deep operand ring
+    // matters more, so staging shrinks first.
+    const long stage = ((long)(128 + p->img_n) * p->kchunk + 1023) & ~1023L;
+    const long staging = (long)img_staging_bytes(*p);
+    const long budget = 227 * 1024 - 1024 - 2304;  // alignment slack, control block
+    int n_staging = 2;
+    long stages = (budget - n_staging * staging) / stage;
+    if (stages < 4) {
+        n_staging = 1;
+        stages = (budget - staging) / stage;
+    }
+    if (const char *e = getenv("XNOR_NN_B200_DEV_STAGING")) {  // development override
+        n_staging = atoi(e);
+        stages = (budget - n_staging * staging) / stage;
+    }
+    if (stages < 2) return;
+    p->img_stages = (int)(stages > 8 ? 8 : stages);
+    p->img_staging = n_staging;
+
+    p->img = true;
 }
 
 void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
@@ -70,13 +160,18 @@ void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
     p->inv_khw = 1.f / p->kh / p->kw;
     p->inv_chw = 1.f / (p->ic * p->kh * p->kw);
 
-    Family f = requested == kAuto ? family_from_env() : requested;
-    const bool walk = frame_walk_ok(*p);
-    if (f == kAuto) f = walk ? kTcgen05 : kPopc;
-    // mma.sync b1 was measured and ruled out (its ceiling is below what the popc kernel
-    // achieves); a request for it is served by popc.
-    if (f == kMmaB1) f = kPopc;
-    if (f == kTcgen05 && !walk) f = kPopc;
+    // The position-tile kernel serves every shape it can: with one tcgen05.commit per four
+    // instructions a tile costs the same whatever its N, so the shape with the fewest tiles wins,
+    // and that kernel's tiles are always 128 x 256 (measured on the five benchmark layers: 36 /
+    // 44 / 68 / 95 us against 45 / 49 / 74 / 109 us). The image-row kernel takes what is left:
+    // paddings as large as the filter, output extents that do not follow from the padding.
+    Family f = requested;
+    if (f != kPopc && f != kTcgen05 && f != kTcgen05Rows) f = family_from_env();
+    const bool frame = frame_walk_ok(*p), rows = image_rows_ok(*p);
+    if (f == kAuto) f = (frame || rows) ? kTcgen05 : kPopc;
+    const bool force_rows = f == kTcgen05Rows;
+    if (force_rows) f = rows ? kTcgen05 : kPopc;
+    if (f == kTcgen05 && !frame && !rows) f = kPopc;
     p->family = f;
 
     const size_t px_in = (size_t)p->mb * p->ih * p->iw;
@@ -91,49 +186,49 @@ void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested) {
     p->hp = p->ih + p->ph;
     p->q_total = (long)p->mb * p->hp * p->wp;
 
-    if (f == kPopc) {
+    auto plan_popc = [&] {
+        p->family = kPopc;
+        p->img = false;
         p->ocp = div_up_i(p->oc, 8) * 8;
         p->bytes[xnor_nn_resource_bin_src] = px_in * p->icw * sizeof(uint32_t);
         p->bytes[xnor_nn_resource_bin_weights] =
             (size_t)p->kh * p->kw * p->icw * p->ocp * sizeof(uint32_t);
-    } else {
-        // K chunk = bytes of one channel group per pipeline stage = the swizzle span. Wide
-        // chunks mean few, fat stages (4 MMAs per barrier round trip at 128 B), which is worth
-        // some zero padding of the channels: 96 channels padded to 128 run the 5x5 AlexNet layer
-        // in 67 us, as three 32-byte chunks in 89 us. Take the widest chunk that pads the
-        // channels by no more than 35 %.
-        p->kchunk = 32;
-        for (int k = 128; k >= 64; k /= 2)
-            if (div_up_i(p->ic, k) * k <= p->ic * 1.35) { p->kchunk = k; break; }
-        if (const char *e = getenv("XNOR_NN_B200_KCHUNK")) {  // tuning override: 32, 64 or 128
-            const int v = atoi(e);
-            if (v == 32 || v == 64 || v == 128) p->kchunk = v;
-        }
-        p->icp = div_up_i(p->ic, p->kchunk) * p->kchunk;
-        // Filter tile = UMMA N: a multiple of 16, at most 256. The filters are split into the
-        // fewest equal tiles and padded (with zero filters) to fill them, so N stays as wide as
-        // possible: the kernel is bound by the instruction stream that issues the MMAs, whose
-        // cost per instruction does not shrink with N (conv4 on 128 images: 32.9 us at N=128
-        // against 26.7 us at N=256).
-        // Exception: when the whole layer is fewer tiles than half the SMs (small minibatches,
-        // e.g. one GPU's share of a sharded batch), halving N doubles the SMs at work without
-        // adding a round of tiles; below N=128 the per-instruction cost eats the gain.
-        const int fewest = div_up_i(p->oc, 256);
-        int n_tiles = fewest;
-        const long m_tiles = (p->q_total + 127) / 128;
-        while (m_tiles * n_tiles * 2 <= sm_count() && div_up_i(p->oc, n_tiles * 2) >= 128)
-            n_tiles *= 2;
-        if (const char *e = getenv("XNOR_NN_B200_NTILES")) {  // tuning override
-            const int v = atoi(e);
-            if (v >= fewest && div_up_i(p->oc, v) >= 16) n_tiles = v;
-        }
-        p->n_tile = div_up_i(div_up_i(p->oc, n_tiles), 16) * 16;
-        p->ocp16 = p->n_tile * n_tiles;
-        p->lead = p->ph * p->wp + p->pw;
-        p->rows = p->lead + p->q_total + 256 + (long)p->kh * p->wp + p->kw;
-        p->bytes[xnor_nn_resource_bin_src] = (size_t)p->rows * p->icp;
-        p->bytes[xnor_nn_resource_bin_weights] = (size_t)p->kh * p->kw * p->ocp16 * p->icp;
+    };
+    if (f == kPopc) {
+        plan_popc();
+        return;
     }
+    // K chunk = bytes of one channel group per pipeline stage = the swizzle span. Wide chunks
+    // mean few, fat stages (4 MMAs per barrier round trip at 128 B), which is worth some zero
+    // padding of the channels: 96 channels padded to 128 run the 5x5 AlexNet layer in 67 us, as
+    // three 32-byte chunks in 89 us. Take the widest chunk that pads the channels by no more
+    // than 35 %.
+    p->kchunk = 32;
+    for (int k = 128; k >= 64; k /= 2)
+        if (div_up_i(p->ic, k) * k <= p->ic * 1.35) { p->kchunk = k; break; }
+    p->icp = div_up_i(p->ic, p->kchunk) * p->kchunk;
+    // Filter tile of the position-tile kernel = its UMMA N: a multiple of 16, at most 256. The
+    // filters are split into the fewest equal tiles and padded (with zero filters) to fill them,
+    // so N stays as wide as possible: the kernel is bound by the instruction stream that issues
+    // the MMAs, whose cost per instruction does not shrink with N. When the whole layer is fewer
+    // tiles than half the SMs, halving N doubles the SMs at work without adding a round of
+    // tiles; below N=128 the per-instruction cost eats the gain.
+    // The same number is the row count of a filter tap in the packed weight matrix, which both
+    // tensor-core kernels read.
+    const int fewest = div_up_i(p->oc, 256);
+    int n_tiles = fewest;
+    const long m_tiles = (p->q_total + 127) / 128;
+    while (m_tiles * n_tiles * 2 <= sm_count() && div_up_i(p->oc, n_tiles * 2) >= 128)
+        n_tiles *= 2;
+    p->n_tile = div_up_i(div_up_i(p->oc, n_tiles), 16) * 16;
+    p->ocp16 = p->n_tile * n_tiles;
+    p->lead = p->ph * p->wp + p->pw;
+    p->rows = p->lead + p->q_total + 256 + (long)p->kh * p->wp + p->kw;
+    p->bytes[xnor_nn_resource_bin_src] = (size_t)p->rows * p->icp;
+    p->bytes[xnor_nn_resource_bin_weights] = (size_t)p->kh * p->kw * p->ocp16 * p->icp;
+    p->img_forced = force_rows || !frame;
+    plan_image_rows(p);
+    if (!p->img && !frame) plan_popc();  // neither tensor-core kernel can serve the shape
 }
 
 }  // namespace xb200

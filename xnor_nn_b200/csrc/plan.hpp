@@ -14,9 +14,9 @@ namespace xb200 {
 // Which convolution kernel consumes the packed operands. The packed layouts differ per family,
 // so the choice is fixed at init and every executor of the descriptor follows it.
 enum Family : int {
-    kPopc = 0,     // bits, LOP3 + POPC on the integer pipe; any stride, padding and format
-    kMmaB1 = 1,    // mma.sync m16n8k256 xor.popc: measured, ruled out, never selected
-    kTcgen05 = 2,  // +-1 int8, tcgen05.mma kind::i8 into tensor memory; stride 1
+    kPopc = 0,          // bits, LOP3 + POPC on the integer pipe; any stride, padding and format
+    kTcgen05 = 2,       // +-1 int8, tcgen05.mma kind::i8 into tensor memory; stride 1
+    kTcgen05Rows = 3,   // request only: the same family, forced onto its image-row kernel
     kAuto = -1,
 };
 
@@ -58,6 +58,25 @@ struct Plan {
     int ocp16;      // output channels rounded up to 16 (UMMA N granularity)
     int n_tile;     // UMMA N per accumulator (<= 256, multiple of 16)
 
+    // ---- tiling of the image-row kernel (kTcgen05, conv_tcgen05_img.cu) ---------------------
+    // That kernel puts 128 filters on the UMMA M side and, on the N side, `img_rows` whole output
+    // rows of one image (img_rows * ow <= 256 positions, rounded up to 16 for the instruction).
+    // Tiles are dealt round-robin to one CTA per SM; the tiles of a last, partly filled round are
+    // cut in two row halves so that they spread over twice as many SMs.
+    bool img;            // the forward pass launches the image-row kernel (else the position-tile one)
+    bool img_forced;     // asked for by name, or the position-tile kernel cannot serve the shape
+    int img_rows;        // output rows per tile
+    int img_n;           // UMMA N of a whole tile
+    int img_row_blocks;  // tiles per image column = ceil(oh / img_rows)
+    int img_m_blocks;    // ceil(oc / 128)
+    int img_tiles;       // mb * img_row_blocks * img_m_blocks
+    int img_whole;       // tiles [0, img_whole) run whole, the rest as two halves each
+    int img_half_rows;   // rows of the first half (0: nothing is split)
+    int img_n_half;      // UMMA N of a half tile
+    int img_grid;        // CTAs launched
+    int img_stages;      // operand pipeline depth
+    int img_staging;     // result staging buffers shared by the four epilogue warps (1, 2 or 4)
+
     size_t bytes[xnor_nn_resource_number];
 };
 
@@ -66,6 +85,16 @@ int div_up_i(int a, int b);
 // Fills a Plan from the descriptor fields and the requested family (kAuto: pick by shape).
 // Never fails: unknown formats are remembered and reported by the executors.
 void make_plan(Plan *p, const xnor_nn_convolution_t *c, Family requested);
+
+// (Re)derives the image-row tiling from the plan's geometry and minibatch; called by make_plan and
+// for every minibatch slice of a plan. Leaves p->img false when the shape does not suit.
+void plan_image_rows(Plan *p);
+// Result staging of the image-row kernel: words per filter row when every filter's run is staged
+// on its own (room for a shift of up to three words; an odd multiple of 4, so that the rows of 32
+// filters spread over the shared-memory banks as well as a multiple of 4 can), and
+// bytes of one staging buffer (32 rows, or a dense 32 x OH*OW block for whole-image tiles).
+int img_staging_row_words(const Plan &p);
+size_t img_staging_bytes(const Plan &p);
 
 const char *family_name(Family f);
 
