@@ -1,18 +1,25 @@
-"""Benchmark of the binary-convolution path: AlexNet conv4, minibatch 256, on N B200s.
+"""Benchmark of the binary-convolution path on N B200s: AlexNet conv4, minibatch 256 (headline),
+and the other four named layers beside it.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--config A..E] [--kernel auto|popc|mma_b1|tcgen05_i8]
+                    [--config A..E|all] [--kernel auto|popc|tcgen05_i8|tcgen05_i8_rows]
 
 A step is one forward pass of the layer (sign-pack + mean-|x| map, K box filter, XNOR/popcount
 convolution with the alpha*K epilogue) over the whole minibatch; with N GPUs the minibatch is
 split into N contiguous slices, one process per GPU, no collective on the data path (strong
-scaling: the total batch stays 256). Rank 0 prints one JSON line.
+scaling: the total batch stays fixed). Rank 0 prints one JSON line.
 
-  value      effective binary TOPS = 2*MB*OC*OH*OW*IC*KH*KW / time, tensors resident in HBM
-  e2e        the same through the C interface with host (pinned) buffers: H2D of the source
-             and D2H of the result inside the timed region
-  roofline   the convolution kernel alone, CUDA events on the launching stream
-  cpu_baseline  the unmodified upstream library (bcast algorithm) on this machine's host cores
+  value / ms_per_step  effective binary TOPS = 2*MB*OC*OH*OW*IC*KH*KW / time, tensors resident in
+             HBM; the K timed steps are repeated as whole regions until 50 ms have been timed
+             and the median region is reported (spread beside it)
+  e2e        the same through the C interface with host (pinned) buffers: H2D of the source and
+             D2H of the result inside the timed region; also upstream's literal three-call
+             sequence with pinned and with pageable buffers
+  roofline   the convolution kernel alone (CUDA events on the launching stream) against the
+             ceiling of its own instruction measured in the same run (pipe_probe)
+  cpu_baseline  the unmodified upstream library (bcast algorithm) on this machine's host cores,
+             timed in a fresh process per executor the way upstream's perf tool does
+  configs    the same figures, briefly, for the other benchmark layers (default: all five)
 
 `--impl reference` times the upstream CPU library on the same layer (rank 0 only).
 Inputs are synthetic (seeded), shapes and value distributions as the layer names say.
@@ -33,33 +40,46 @@ if ROOT not in sys.path:
 
 from xnor_nn_b200 import synth  # noqa: E402
 
+# Cores this process may run on, taken before any OpenMP runtime is loaded: with OMP_PROC_BIND set
+# the runtime pins the calling thread to one core, after which the affinity mask says "1".
+HOST_CPUS = len(os.sched_getaffinity(0))
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+MIN_TIMED_MS = 50.0
 
 
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="B", choices=list(synth.CONFIGS))
-    ap.add_argument("--kernel", default="auto", choices=["auto", "popc", "mma_b1", "tcgen05_i8"])
-    ap.add_argument("--cpu-seconds", type=float, default=12.0,
-                    help="budget of the CPU baseline leg")
+    ap.add_argument("--config", default="B", choices=list(synth.CONFIGS) + ["all"],
+                    help="headline layer; `all` = B with every other layer in `configs`")
+    ap.add_argument("--kernel", default="auto",
+                    choices=["auto", "popc", "tcgen05_i8", "tcgen05_i8_rows"])
+    ap.add_argument("--only", action="store_true", help="no `configs` array, headline layer only")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-probe", action="store_true", help="skip the pipe-rate probe")
+    ap.add_argument("--passes", type=int, default=0,
+                    help="profiler mode: run this many forward passes of the layer on device "
+                         "tensors (optionally --minibatch images) and exit without timing")
+    ap.add_argument("--minibatch", type=int, default=0, help="with --passes: images per pass")
+    ap.add_argument("--chain", action="store_true",
+                    help="time AlexNet conv3 -> conv4 -> conv5 layer by layer and as one chained "
+                         "call (xnor_nn_b200_forward_chain), print one JSON line and exit")
     ap.add_argument("--graph", action="store_true",
                     help="replay the step from CUDA graphs instead of calling the library")
     return ap.parse_args()
 
 
-def binary_ops(L, mb):
-    return 2.0 * mb * L.oc * conv_out(L)[0] * conv_out(L)[1] * L.ic * L.kh * L.kw
-
-
 def conv_out(L):
     return ((L.ih + 2 * L.pw - L.kh) // L.sh + 1, (L.iw + 2 * L.pw - L.kw) // L.sw + 1)
+
+
+def binary_ops(L, mb):
+    oh, ow = conv_out(L)
+    return 2.0 * mb * L.oc * oh * ow * L.ic * L.kh * L.kw
 
 
 def pipe_probe():
@@ -75,18 +95,25 @@ def pipe_probe():
         return None
 
 
-# DRAM bytes of one convolution launch on the benchmark layer, from the ncu capture summarised
-# in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum): the packed operands are read once,
-# the 44 MB result is still in L2 when the kernel ends.
-NCU_CONV_TRAFFIC = {("B", "tcgen05_i8"): 20.37e6 + 0.31e6}
-
-
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             return json.load(f), "measured"
     return dict(FALLBACK_PEAKS), "fallback"
+
+
+def captured_traffic(cfg, kernel_name):
+    """DRAM bytes of one convolution launch taken from a profiler capture, if one is on record
+    for this layer and kernel in bench_traffic.json (written beside the capture's summary);
+    else None. Nothing is assumed: no record, no number."""
+    path = os.path.join(ROOT, "bench_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f).get("%s/%s" % (cfg, kernel_name))
+    except (OSError, ValueError):
+        return None
+    return rec
 
 
 # ---- clocks ------------------------------------------------------------------------------------
@@ -134,11 +161,11 @@ class ClockSampler:
                 except ValueError:
                     pass
             return out
-        inside = parse_rows([r for r in self.rows if t0 <= r[0] <= t1 + 0.15])
+        inside = parse_rows([r for r in self.rows if t0 <= r[0] <= t1])
         window = "timed region"
         if not inside:
-            inside = parse_rows(self.rows)
-            window = "whole run (timed region shorter than the sampling period)"
+            inside = parse_rows([r for r in self.rows if t0 <= r[0] <= t1 + 0.15])
+            window = "timed region + 150 ms (the region is shorter than the sampling period)"
         if not inside:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0,
                     "window": "nvidia-smi unavailable"}
@@ -152,16 +179,31 @@ class ClockSampler:
 
 # ---- reference arm / CPU baseline ----------------------------------------------------------------
 
-def upstream_forward_seconds(L, mb, budget_s, steps=None, warmup=1, threads=None):
-    """Seconds per forward pass (binarize_data + calculate_k + forward, what upstream's
-    Convolution::forward runs) of the unmodified upstream library, bcast algorithm, all host
-    threads, on `mb` images of layer L. Timed like upstream's perf harness
-    (test/perf/test_simple_net.cpp:39-60): wall clock around the executor calls."""
+def host_threads(want=None):
+    """OpenMP threads the upstream library will use: all cores this process may run on, or
+    `want`. (A launcher such as torchrun exports OMP_NUM_THREADS=1 for its workers; the CPU arm is
+    meant to use the whole host, so the team size is set explicitly.)"""
+    try:
+        import ctypes
+        omp = ctypes.CDLL("libgomp.so.1")
+        if want is None:
+            want = HOST_CPUS
+        omp.omp_set_num_threads(want)
+        return omp.omp_get_max_threads()
+    except OSError:
+        return os.cpu_count()
+
+
+def upstream_times(L, cfg_name, mb, steps, warmup, threads=None):
+    """Milliseconds per call of upstream's three per-minibatch executors (bcast algorithm) on
+    `mb` images of layer L, measured the way upstream's perf tool measures them
+    (test/perf/test_simple_net.cpp:32-60,130-144): every timed call is preceded by a pass that
+    dirties a buffer larger than the last-level cache slices the call will use, and the clock
+    runs around the call only. Returns (dict of medians in ms, threads used)."""
     import ctypes as C
     from oracle.pyoracle import UpstreamRef, UpstreamConv
     ref = UpstreamRef()
-    host_threads(threads)
-    cfg_name = [k for k, v in synth.CONFIGS.items() if v.name == L.name][0]
+    used = host_threads(threads)
     src, w = synth.make_inputs(cfg_name, mb=mb)
     c = UpstreamConv()
     assert ref.lib.xnor_nn_init_convolution(C.byref(c), 1, 0, 2, 0, mb, L.oc, L.ic, L.ih, L.iw,
@@ -171,86 +213,196 @@ def upstream_forward_seconds(L, mb, budget_s, steps=None, warmup=1, threads=None
     dst = np.empty(mb * c.oc * c.oh * c.ow, np.float32)
     res[0], res[1], res[2] = src.ctypes.data, w.ctypes.data, dst.ctypes.data
     assert c.binarize_weights(C.addressof(c), res) == 0
-
-    def one():
-        t0 = time.perf_counter()
-        for ex in (c.binarize_data, c.calculate_k, c.forward):
+    trash = np.zeros(64 << 20, np.uint8)  # upstream dirties 16 MB; server L3s are larger
+    out = {}
+    for name in ("binarize_data", "calculate_k", "forward"):
+        ex = getattr(c, name)
+        times = []
+        for i in range(warmup + steps):
+            trash += 1
+            t0 = time.perf_counter()
             assert ex(C.addressof(c), res) == 0
-        return time.perf_counter() - t0
-
-    for _ in range(warmup):
-        first = one()
-    times = []
-    if steps is None:
-        steps = max(1, min(50, int(budget_s / max(first, 1e-6))))
-    for _ in range(steps):
-        times.append(one())
+            dt = time.perf_counter() - t0
+            if i >= warmup:
+                times.append(dt)
+        out[name] = float(np.median(times)) * 1e3
     ref.lib.xnor_nn_free_resources(res)
     ref.lib.xnor_nn_destroy_convolution(C.byref(c))
-    return float(np.sum(times)), steps
+    return out, used
 
 
-def host_threads(want=None):
-    """OpenMP threads the upstream library will use: all cores this process may run on, or
-    `want`. (A launcher such as torchrun exports OMP_NUM_THREADS=1 for its workers; the CPU arm is
-    meant to use the whole host, so the team size is set explicitly.)"""
-    try:
-        import ctypes
-        omp = ctypes.CDLL("libgomp.so.1")
-        if want is None:
-            want = len(os.sched_getaffinity(0))
-        omp.omp_set_num_threads(want)
-        return omp.omp_get_max_threads()
-    except OSError:
-        return os.cpu_count()
-
-
-def run_reference(args, L, rank):
-    if rank != 0:
-        return
+def reference_line(args, cfg_name, L):
+    """The JSON object of the reference arm for one layer (upstream library, all host threads)."""
     from oracle.pyoracle import UpstreamRef
     if not UpstreamRef.available():
-        print(json.dumps({"impl": "reference",
-                          "unavailable": "oracle/_ref/libxnor_nn_ref.so was not built"}))
-        return
-    # Bounded sample: the full layer is ~0.1-1 s per pass on a server CPU, so each step is the
-    # whole minibatch unless that would take minutes.
-    probe, _ = upstream_forward_seconds(L, min(L.mb, 8), 0, steps=1, warmup=1)
-    per_image = probe / min(L.mb, 8)
-    budget = 150.0
+        return {"impl": "reference",
+                "unavailable": "oracle/_ref/libxnor_nn_ref.so was not built"}
+    # Bounded sample: the whole minibatch unless that would take minutes.
+    probe, _ = upstream_times(L, cfg_name, min(L.mb, 8), 1, 1)
+    per_image = sum(probe.values()) * 1e-3 / min(L.mb, 8)
     mb = L.mb
-    while mb > 8 and per_image * mb * (args.steps + args.warmup) > budget:
+    while mb > 8 and per_image * mb * (args.steps + max(1, args.warmup)) > 100.0:
         mb //= 2
-    total, steps = upstream_forward_seconds(L, mb, 0, steps=args.steps, warmup=max(1, args.warmup))
-    sec = total / steps
-    tops = binary_ops(L, mb) / sec / 1e12
-    threads = host_threads()
-    sample = "%d of %d images per step, %d steps" % (mb, L.mb, steps)
-    print(json.dumps({
+    t, threads = upstream_times(L, cfg_name, mb, args.steps, max(1, args.warmup))
+    scale = L.mb / mb
+    ms = sum(t.values()) * scale
+    tops = binary_ops(L, L.mb) / (ms * 1e-3) / 1e12
+    sample = "%d of %d images per step, %d steps" % (mb, L.mb, args.steps)
+    return {
         "impl": "reference", "metric": "effective_binary_tops", "value": tops, "unit": "TOPS",
-        "n_gpus": args.gpus, "steps": steps, "warmup": max(1, args.warmup),
-        "ms_per_step": sec * 1e3 * (L.mb / mb), "higher_is_better": True, "scaling": "strong",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": max(1, args.warmup),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "u16", "data": "synthetic",
         "config": {"workload": L.name, "algorithm": "upstream bcast, XNOR_NN_ISA=2",
-                   "sample": sample},
+                   "sample": sample, "omp_threads": threads,
+                   "omp_proc_bind": os.environ.get("OMP_PROC_BIND", "unset"),
+                   "protocol": "per executor, cache dirtied before every timed call, median"},
+        "executors_ms": {k: v * scale for k, v in t.items()},
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": threads, "kind": "reference",
                          "sample": sample},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0}))
+        "gpu_launches": 0}
+
+
+def run_reference(args, cfg_name, L, rank):
+    if rank != 0:
+        return
+    print(json.dumps(reference_line(args, cfg_name, L)))
+
+
+def cpu_baseline_subprocess(cfg_name, steps):
+    """The reference arm in a process of its own (no CUDA context, no torch threads, threads
+    bound to neighbouring cores) so that it measures what `--impl reference` measures."""
+    env = dict(os.environ)
+    env.pop("OMP_NUM_THREADS", None)
+    env.setdefault("OMP_PROC_BIND", "close")
+    env.setdefault("XNOR_NN_ISA", "2")
+    try:
+        out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference",
+                              "--config", cfg_name, "--steps", str(steps), "--warmup", "2"],
+                             capture_output=True, text=True, timeout=600, env=env).stdout
+        d = json.loads(out.strip().splitlines()[-1])
+    except (OSError, ValueError, IndexError, subprocess.TimeoutExpired):
+        return None
+    if "unavailable" in d:
+        return None
+    return {"value": d["value"], "unit": "TOPS", "cores": d["cpu_baseline"]["cores"],
+            "kind": "reference", "sample": d["cpu_baseline"]["sample"],
+            "ms_per_step": d["ms_per_step"], "executors_ms": d["executors_ms"],
+            "omp_proc_bind": d["config"]["omp_proc_bind"], "process": "fresh subprocess"}
 
 
 # ---- our arm -------------------------------------------------------------------------------------
 
-def run_ours(args, L, rank, world, local_rank):
-    import torch
-    import xnor_nn_b200 as xb
+class Layer:
+    """One benchmark layer on this rank's GPU: its slice of the minibatch, rotating device
+    tensors, and the timing helpers."""
 
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    def __init__(self, xb, torch, cfg_name, kernel, rank, world):
+        from xnor_nn_b200.sharding import shard_range
+        self.xb, self.torch, self.cfg = xb, torch, cfg_name
+        L = self.L = synth.CONFIGS[cfg_name]
+        first, last = shard_range(L.mb, rank, world)
+        self.first, self.mb = first, last - first
+        self.oh, self.ow = conv_out(L)
+        self.stream = torch.cuda.current_stream()
+        self.kernel_name = None
+        self.n_src = self.n_dst = self.step_bytes = self.sets = 0
+        if self.mb == 0:  # more GPUs than images: this rank only keeps the others company
+            self.conv = None
+            return
+        self.src_np, self.w_np = synth.make_inputs(cfg_name, mb=self.mb, first_image=first)
+        self.conv = xb.Convolution(xb.ALGORITHM_BCAST, xb.NCHW, xb.OIHW, xb.NCHW, self.mb, L.oc,
+                                   L.ic, L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw,
+                                   self.w_np, kernel=kernel)
+        self.kernel_name = xb.KERNEL_NAMES[self.conv.kernel]
+        self.conv.set_stream(self.stream.cuda_stream)
+        # Rotating device buffers: consecutive steps touch different tensors and one full
+        # rotation exceeds L2 several times over, so no step finds its input or output cached.
+        self.n_src, self.n_dst = self.src_np.size, self.mb * L.oc * self.oh * self.ow
+        self.step_bytes = 4 * (self.n_src + self.n_dst)
+        self.sets = min(48, max(2, int(np.ceil(3.2 * L2_BYTES / self.step_bytes)) + 1))
+        self.d_src = [torch.from_numpy(self.src_np).cuda() for _ in range(self.sets)]
+        self.d_dst = [torch.empty(self.n_dst, dtype=torch.float32, device="cuda")
+                      for _ in range(self.sets)]
 
+    def step(self, i):
+        if self.conv is not None:
+            self.conv.forward(self.d_src[i % self.sets], self.d_dst[i % self.sets])
+
+    def conv_only(self, i):
+        import ctypes as C
+        if self.conv is None:
+            return
+        xb = self.xb
+        self.conv._set(xb.SLOT_USER_DST, self.d_dst[i % self.sets])
+        st = self.conv.c.forward(C.addressof(self.conv.c), self.conv.res)
+        assert st == xb.SUCCESS, xb.last_error()
+
+    def bin_only(self, i):
+        import ctypes as C
+        if self.conv is None:
+            return
+        xb = self.xb
+        self.conv._set(xb.SLOT_USER_SRC, self.d_src[i % self.sets])
+        st = xb.lib().xnor_nn_b200_binarize(C.byref(self.conv.c), self.conv.res)
+        assert st == xb.SUCCESS, xb.last_error()
+
+    def region_ms(self, fn, n, offset=0):
+        """Device time of n consecutive calls of fn, CUDA events on the launching stream."""
+        torch = self.torch
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(self.stream)
+        for i in range(n):
+            fn(offset + i)
+        b.record(self.stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    def timed(self, fn, n, min_ms=10.0):
+        """Median milliseconds per call over regions of n calls, at least min_ms timed."""
+        for i in range(3):
+            fn(i)
+        self.torch.cuda.synchronize()
+        per, total, k = [], 0.0, 0
+        while total < min_ms or len(per) < 3:
+            ms = self.region_ms(fn, n, k * n)
+            per.append(ms / n)
+            total += ms
+            k += 1
+            if k >= 200:
+                break
+        return float(np.median(per))
+
+    def parity_ok(self, oracle_mod):
+        """First and last image of this rank's slice against the CPU oracle (outside any timed
+        region): integer-exact results scaled in upstream's order, so the floats must agree to
+        1e-4 relative."""
+        torch = self.torch
+        L = self.L
+        self.step(0)
+        torch.cuda.synchronize()
+        got = self.d_dst[0].cpu().numpy()
+        per = L.oc * self.oh * self.ow
+        orc = oracle_mod.Oracle()
+        for img in sorted({0, self.mb - 1}):
+            s = oracle_mod.Shape.make(1, L.oc, L.ic, L.ih, L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw)
+            want = orc.convolution(s, self.src_np[img:img + 1], self.w_np)["dst"]
+            err = np.abs(got[img * per:(img + 1) * per] - want)
+            if not np.all(err <= 1e-4 * np.abs(want)):
+                return False
+        return True
+
+    def close(self):
+        if self.conv is not None:
+            self.conv.close()
+        self.d_src = self.d_dst = None
+        self.torch.cuda.empty_cache()
+
+
+def measure_layer(xb, torch, args, cfg_name, kernel, rank, world, dist, probe, brief):
+    """All figures of one layer. `brief` (the `configs` entries) leaves out the literal
+    three-call sequence, the clocks and the CUDA-graph option."""
     def barrier():
         if dist is not None:
             dist.barrier()
@@ -263,200 +415,273 @@ def run_ours(args, L, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    from xnor_nn_b200.sharding import shard_range
-    first, last = shard_range(L.mb, rank, world)
-    mb = last - first
-    oh, ow = conv_out(L)
-    kernel = {"auto": xb.KERNEL_AUTO, "popc": xb.KERNEL_POPC, "mma_b1": xb.KERNEL_MMA_B1,
-              "tcgen05_i8": xb.KERNEL_TCGEN05_I8}[args.kernel]
+    lay = Layer(xb, torch, cfg_name, kernel, rank, world)
+    L, mb = lay.L, lay.mb
+    steps = args.steps if not brief else max(20, min(args.steps, 100))
 
-    src_np, w_np = synth.make_inputs(args.config, mb=mb, first_image=first)
-    conv = xb.Convolution(xb.ALGORITHM_BCAST, xb.NCHW, xb.OIHW, xb.NCHW, mb, L.oc, L.ic, L.ih,
-                          L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, w_np, kernel=kernel)
-    kernel_name = xb.KERNEL_NAMES[conv.kernel]
-    stream = torch.cuda.current_stream()
-    conv.set_stream(stream.cuda_stream)
+    # parity of this rank's slice, outside the timed regions
+    ok = True
+    if mb > 0:
+        from oracle import pyoracle  # the checker, outside every timed region
+        ok = lay.parity_ok(pyoracle)
+    if dist is not None:
+        t = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = bool(t.item())
 
-    # Rotating device buffers: consecutive steps touch different tensors and one full rotation
-    # exceeds L2 several times over, so no step finds its input or output cached.
-    n_src, n_dst = src_np.size, mb * L.oc * oh * ow
-    step_bytes = 4 * (n_src + n_dst)
-    sets = max(2, int(np.ceil(3.2 * L2_BYTES / step_bytes)) + 1)
-    d_src = [torch.from_numpy(src_np).cuda() for _ in range(sets)]
-    d_dst = [torch.empty(n_dst, dtype=torch.float32, device="cuda") for _ in range(sets)]
-
-    def eager_step(i):
-        conv.forward(d_src[i % sets], d_dst[i % sets])
-
-    # The step is two kernel launches behind a C call. --graph replays it from a CUDA graph (one
-    # per tensor set, captured once), which takes the host out of the loop; the same kernels run
-    # either way. Plain calls are the default because they are faster here: consecutive launches
-    # of one stream overlap their set-up with the predecessor's tail, consecutive graph launches
-    # do not (54.3 vs 55.4 us per step on conv4).
     graphs = None
     launches_per_step = None
-    if args.graph:
+    step = lay.step
+    if args.graph and not brief:
         for i in range(2):
-            eager_step(i)
+            lay.step(i)
         torch.cuda.synchronize()
         graphs = []
         side = torch.cuda.Stream()
-        conv.set_stream(side.cuda_stream)  # before capture starts: switching streams synchronises
-        for k in range(sets):
+        lay.conv.set_stream(side.cuda_stream)  # before capture starts: switching synchronises
+        for k in range(lay.sets):
             g = torch.cuda.CUDAGraph()
             before = xb.kernel_launches()
             with torch.cuda.graph(g, stream=side):
-                conv.forward(d_src[k], d_dst[k])
+                lay.conv.forward(lay.d_src[k], lay.d_dst[k])
             launches_per_step = xb.kernel_launches() - before
             graphs.append(g)
-        conv.set_stream(stream.cuda_stream)
+        lay.conv.set_stream(lay.stream.cuda_stream)
 
-    def step(i):
-        if graphs is not None:
-            graphs[i % sets].replay()
-        else:
-            eager_step(i)
+        def step(i):
+            graphs[i % lay.sets].replay()
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 and not brief else None
     for i in range(max(3, args.warmup)):
         step(i)
     barrier()
+    # Regions of exactly `steps` steps, each bracketed by a barrier and a device synchronise and
+    # timed as the slowest rank, repeated until MIN_TIMED_MS have been timed.
     launches0 = xb.kernel_launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall0 = time.time()
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
-    torch.cuda.synchronize()
+    regions, total = [], 0.0
+    while (total < MIN_TIMED_MS or len(regions) < 3) and len(regions) < 400:
+        barrier()
+        ms = max_over_ranks(lay.region_ms(step, steps, len(regions) * steps))
+        regions.append(ms / steps)
+        total += ms
     t_wall1 = time.time()
+    barrier()
     launches = xb.kernel_launches() - launches0
     if graphs is not None:
-        launches = launches_per_step * args.steps  # kernel nodes replayed inside the timed region
-    barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
-    ms_step = ms_total / args.steps
+        launches = launches_per_step * steps * len(regions)
+    ms_step = float(np.median(regions))
     value = binary_ops(L, L.mb) / (ms_step * 1e-3) / 1e12
 
-    # ---- the dominant kernel alone (convolution), same rotation -----------------------------
-    import ctypes as C
-    conv._set(xb.SLOT_USER_SRC, d_src[0])
-
-    def conv_only(i):
-        conv._set(xb.SLOT_USER_DST, d_dst[i % sets])
-        st = conv.c.forward(C.addressof(conv.c), conv.res)
-        assert st == xb.SUCCESS, xb.last_error()
-
-    def bin_only(i):
-        conv._set(xb.SLOT_USER_SRC, d_src[i % sets])
-        st = conv.c.binarize_data(C.addressof(conv.c), conv.res)
-        assert st == xb.SUCCESS, xb.last_error()
-
-    def timed(fn, n):
-        for i in range(3):
-            fn(i)
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream)
-        for i in range(n):
-            fn(i)
-        b.record(stream)
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / n
-
-    n_k = max(20, min(args.steps, 200))
-    conv_ms = timed(conv_only, n_k)
-    bin_ms = timed(bin_only, n_k)
+    # ---- the two kernels alone, same rotation (rank 0's slice is never empty) ---------------
+    if lay.conv is not None:
+        lay.conv._set(xb.SLOT_USER_SRC, lay.d_src[0])
+    n_k = max(20, min(steps, 200))
+    conv_ms = lay.timed(lay.conv_only, n_k) if lay.conv is not None else 0.0
+    bin_ms = lay.timed(lay.bin_only, n_k) if lay.conv is not None else 0.0
+    if rank != 0:  # only rank 0 reports; the others still take part in the collectives below
+        conv_ms = bin_ms = 1.0
+        lay.kernel_name = lay.kernel_name or "tcgen05_i8"
     # compulsory bytes of the packing pass: 4 B per source element in, 1 B (tensor-core family)
-    # or 1 bit (bit families) per element out
-    bin_bytes = 4.0 * n_src + (n_src if kernel_name == "tcgen05_i8" else n_src / 8.0)
+    # or 1 bit (integer-pipe family) per element out, plus the mean-|x| map
+    tc = (lay.kernel_name or "tcgen05").startswith("tcgen05")
+    bin_bytes = 4.0 * lay.n_src + (lay.n_src if tc else lay.n_src / 8.0) + 4.0 * mb * L.ih * L.iw
     pk, pk_kind = peaks()
-    probe = pipe_probe() if rank == 0 and not args.no_probe else None
     conv_tops = binary_ops(L, mb) / (conv_ms * 1e-3) / 1e12
-    probe_peak = None
-    if kernel_name == "tcgen05_i8":
-        # 8-bit operands issue at twice the 16-bit rate on the same tensor pipe
-        peak = 2.0 * pk["bf16_tflops"]
-        peak_note = "2 x %s bf16 dense burst (8-bit operands)" % pk_kind
+    if tc:
+        peak = probe.get("tcgen05_i8_tops") if probe else None
+        peak_note = "tcgen05.mma kind::i8 ceiling measured in this run (pipe_probe)"
         bound = "tensor"
-        probe_peak = probe.get("tcgen05_i8_tops") if probe else None
     else:
-        key = "mma_b1_binary_tops" if kernel_name == "mma_b1" else "popc_binary_tops"
-        peak = probe.get(key) if probe else None
-        peak_note = "pipe_probe, measured in this run (no MEASURED_PEAKS entry for this pipe)"
-        bound = "tensor" if kernel_name == "mma_b1" else "int_pipe"
-        probe_peak = peak
-    roofline = {"kernel": "conv_" + kernel_name, "bound": bound, "achieved": conv_tops,
+        peak = probe.get("popc_binary_tops") if probe else None
+        peak_note = "LOP3+POPC ceiling measured in this run (pipe_probe)"
+        bound = "int_pipe"
+    alt_peak = 2.0 * pk["bf16_tflops"] if tc else None
+    traffic = captured_traffic(cfg_name, lay.kernel_name) if world == 1 else None
+    roofline = {"kernel": "conv_" + lay.kernel_name, "bound": bound, "achieved": conv_tops,
                 "peak": peak, "unit": "TFLOP/s", "frac": (conv_tops / peak) if peak else None,
-                "traffic": NCU_CONV_TRAFFIC.get((args.config, kernel_name)) if world == 1 else None,
+                "traffic": traffic["bytes"] if traffic else None,
+                "traffic_source": traffic.get("source") if traffic else None,
                 "peak_source": peak_note, "ms": conv_ms,
-                "frac_of_probe_peak": (conv_tops / probe_peak) if probe_peak else None,
-                "pipe_probe": probe,
-                "binarize": {"bound": "hbm", "achieved": bin_bytes / (bin_ms * 1e-3) / 1e9,
+                "frac_of_2x_bf16_%s" % pk_kind: (conv_tops / alt_peak) if alt_peak else None,
+                "binarize": {"kernel": "sign-pack with the mean-|x| map (the pass the step runs)",
+                             "bound": "hbm", "achieved": bin_bytes / (bin_ms * 1e-3) / 1e9,
                              "peak": pk["hbm_gbs"], "unit": "GB/s",
                              "frac": bin_bytes / (bin_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
                              "ms": bin_ms, "peak_source": pk_kind,
-                             "bytes": "fp32 source read once + packed activations written"}}
+                             "bytes": "fp32 source read once + packed activations and map written"}}
 
     # ---- end to end: host buffers through the C interface -----------------------------------
-    conv.synchronize()
-    h_src = torch.from_numpy(src_np).pin_memory()
-    h_dst = torch.empty(n_dst, dtype=torch.float32).pin_memory()
-    e2e_steps = max(3, min(args.steps, 30))
-    for _ in range(3):
-        conv.forward(h_src, h_dst)
-    barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record(stream)
-    for _ in range(e2e_steps):
-        conv.forward(h_src, h_dst)  # returns when h_dst is complete
-    b.record(stream)
-    torch.cuda.synchronize()
-    barrier()
-    e2e_ms = max_over_ranks(a.elapsed_time(b)) / e2e_steps
-    e2e = {"value": binary_ops(L, L.mb) / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
-           "h2d_bytes_per_step": 4 * n_src, "d2h_bytes_per_step": 4 * n_dst, "ms_per_step": e2e_ms,
-           "call": "xnor_nn_b200_forward (host pointers, pinned)"}
+    if lay.conv is not None:
+        lay.conv.synchronize()
+        h_src = torch.from_numpy(lay.src_np).pin_memory()
+        h_dst = torch.empty(lay.n_dst, dtype=torch.float32).pin_memory()
+    e2e_steps = max(3, min(steps, 20))
+
+    def e2e_ms(which, src, dst):
+        call = getattr(lay.conv, which) if lay.conv is not None else (lambda a, b: None)
+        for _ in range(2):
+            call(src, dst)
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(lay.stream)
+        for _ in range(e2e_steps):
+            call(src, dst)  # returns when dst is complete
+        b.record(lay.stream)
+        torch.cuda.synchronize()
+        barrier()
+        return max_over_ranks(a.elapsed_time(b)) / e2e_steps
+
+    if lay.conv is None:
+        h_src = h_dst = None
+    one_call = e2e_ms("forward", h_src, h_dst)
+    e2e = {"value": binary_ops(L, L.mb) / (one_call * 1e-3) / 1e12, "unit": "TOPS",
+           "h2d_bytes_per_step": 4 * lay.n_src, "d2h_bytes_per_step": 4 * lay.n_dst,
+           "ms_per_step": one_call, "call": "xnor_nn_b200_forward (host pointers, pinned)"}
+    if not brief:
+        e2e["three_calls_pinned_ms"] = e2e_ms("forward_stepwise", h_src, h_dst)
+        p_src = lay.src_np if lay.conv is not None else None
+        p_dst = np.empty(lay.n_dst, np.float32) if lay.conv is not None else None
+        e2e["three_calls_pageable_ms"] = e2e_ms("forward_stepwise", p_src, p_dst)
+        e2e["one_call_pageable_ms"] = e2e_ms("forward", p_src, p_dst)
+        e2e["three_calls"] = ("binarize_data, calculate_k, forward through the executor pointers, "
+                              "as upstream's wrapper issues them")
 
     clocks = None
     if sampler:
-        time.sleep(0.12)
         sampler.stop()
         clocks = sampler.summary(t_wall0, t_wall1)
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        from oracle.pyoracle import UpstreamRef
-        if UpstreamRef.available():
-            total, steps = upstream_forward_seconds(L, L.mb, args.cpu_seconds)
-            cpu = {"value": binary_ops(L, L.mb) / (total / steps) / 1e12, "unit": "TOPS",
-                   "cores": host_threads(), "kind": "reference",
-                   "ms_per_step": total / steps * 1e3,
-                   "sample": "full minibatch (%d images), %d passes, upstream bcast, "
-                             "XNOR_NN_ISA=2" % (L.mb, steps)}
-            # the same library on one thread, on a few images (it scales with the image count)
-            few = min(L.mb, 8)
-            t1, n1 = upstream_forward_seconds(L, few, 0, steps=2, warmup=1, threads=1)
-            cpu["one_thread"] = {"value": binary_ops(L, few) / (t1 / n1) / 1e12, "unit": "TOPS",
-                                 "ms_per_step": t1 / n1 * 1e3 * (L.mb / few),
-                                 "sample": "%d of %d images, scaled" % (few, L.mb)}
-            host_threads()
+    line = {
+        "metric": "effective_binary_tops", "value": value, "unit": "TOPS", "n_gpus": world,
+        "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+        "ms_per_step_min": float(np.min(regions)), "ms_per_step_max": float(np.max(regions)),
+        "timed_regions": len(regions), "timed_ms": total,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "s8" if tc else "u32", "data": "synthetic",
+        "config": {"workload": L.name, "minibatch": L.mb, "images_per_gpu": mb,
+                   "kernel": lay.kernel_name, "parallelism": "minibatch slices x%d" % world,
+                   "l2": ("inputs larger than L2: %d rotating tensor sets of %.1f MB"
+                          if lay.sets * lay.step_bytes > 2 * L2_BYTES else
+                          "%d rotating tensor sets of %.2f MB: smaller than L2, a layer this "
+                          "small is bound by latency, not by memory")
+                         % (lay.sets, lay.step_bytes / 1e6),
+                   "launch": "cuda graph replay, one graph per tensor set"
+                             if graphs is not None else "plain calls"},
+        "parity_checked": ok,
+        "roofline": roofline, "e2e": e2e, "clocks": clocks, "gpu_launches": int(launches)}
+    lay.close()
+    return line
 
+
+def chain_line(xb, torch, mb, reps):
+    """AlexNet's conv3 -> conv4 -> conv5 (13x13, 3x3, pad 1: 256 -> 384 -> 256 -> 256 channels)
+    layer by layer and as one chained call, tensors resident on the device, microseconds per
+    pass (six rotating tensor sets so that a pass does not find its inputs in L2)."""
+    channels = (256, 384, 256, 256)
+    convs = []
+    for i in range(3):
+        ic, oc = channels[i], channels[i + 1]
+        w = synth.normal(0xBEEF0000 + i, oc * ic * 9, 0.05)
+        convs.append(xb.Convolution(xb.ALGORITHM_BCAST, xb.NCHW, xb.OIHW, xb.NCHW, mb, oc, ic, 13,
+                                    13, 3, 3, 1, 1, 1, 1, w))
+    stream = torch.cuda.current_stream().cuda_stream
+    for cv in convs:
+        cv.set_stream(stream)
+    sets = 6
+    bufs = [[torch.randn(mb * c * 169, device="cuda") for c in channels] for _ in range(sets)]
+
+    def timed(fn):
+        for i in range(30):
+            fn(bufs[i % sets])
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(reps):
+            fn(bufs[i % sets])
+        t1.record()
+        torch.cuda.synchronize()
+        return round(t0.elapsed_time(t1) / reps * 1e3, 1)
+
+    def separate(n):
+        def run(b):
+            for i in range(n):
+                convs[i].forward(b[i], b[i + 1])
+        return run
+
+    def chained(n):
+        return lambda b: xb.forward_chain(convs[:n], b[0], b[n])
+
+    print(json.dumps({
+        "chain": "alexnet conv3 -> conv4 -> conv5", "minibatch": mb, "reps": reps,
+        "unit": "us per pass",
+        "conv3_conv4": {"layer_by_layer": timed(separate(2)), "chained": timed(chained(2))},
+        "conv3_conv4_conv5": {"layer_by_layer": timed(separate(3)), "chained": timed(chained(3))}}))
+    for cv in convs:
+        cv.close()
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import xnor_nn_b200 as xb
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    kernel = {"auto": xb.KERNEL_AUTO, "popc": xb.KERNEL_POPC, "tcgen05_i8": xb.KERNEL_TCGEN05_I8,
+              "tcgen05_i8_rows": xb.KERNEL_TCGEN05_I8_ROWS}[args.kernel]
+    head = "B" if args.config == "all" else args.config
+    if args.passes:
+        # a handful of launches for a profiler: few warm-ups, nothing else on the device
+        L = synth.CONFIGS[head]
+        mb = args.minibatch or L.mb
+        src, w = synth.make_inputs(head, mb=mb)
+        conv = xb.Convolution(xb.ALGORITHM_BCAST, xb.NCHW, xb.OIHW, xb.NCHW, mb, L.oc, L.ic, L.ih,
+                              L.iw, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, w, kernel=kernel)
+        d_src = torch.from_numpy(src).cuda()
+        d_dst = torch.empty(int(np.prod(conv.out_shape)), device="cuda")
+        for _ in range(args.passes):
+            conv.forward(d_src, d_dst)
+        conv.synchronize()
+        print("ok %s mb=%d passes=%d" % (xb.KERNEL_NAMES[conv.kernel], mb, args.passes))
+        conv.close()
+        return
+    if args.chain:
+        chain_line(xb, torch, args.minibatch or 256, max(20, min(args.steps, 200)))
+        return
+    others = [] if args.only else [c for c in synth.CONFIGS if c != head]
+    probe = pipe_probe() if rank == 0 and not args.no_probe else None
+    if dist is not None:  # every rank computes the fraction of the same ceiling
+        box = [probe]
+        dist.broadcast_object_list(box, src=0)
+        probe = box[0]
+
+    line = measure_layer(xb, torch, args, head, kernel, rank, world, dist, probe, brief=False)
+    line["roofline"]["pipe_probe"] = probe
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_subprocess(head, 10)
+    else:
+        line["cpu_baseline"] = None
+    configs = []
+    for cfg in others:
+        d = measure_layer(xb, torch, args, cfg, kernel, rank, world, dist, probe, brief=True)
+        entry = {"config": cfg, "workload": d["config"]["workload"],
+                 "images_per_gpu": d["config"]["images_per_gpu"], "kernel": d["config"]["kernel"],
+                 "ms_per_step": d["ms_per_step"], "value": d["value"], "unit": "TOPS",
+                 "conv_ms": d["roofline"]["ms"], "conv_tops": d["roofline"]["achieved"],
+                 "conv_frac": d["roofline"]["frac"], "binarize_ms": d["roofline"]["binarize"]["ms"],
+                 "binarize_frac": d["roofline"]["binarize"]["frac"],
+                 "e2e_ms": d["e2e"]["ms_per_step"], "parity_checked": d["parity_checked"]}
+        if rank == 0 and world == 1 and not args.no_cpu_baseline:
+            cpu = cpu_baseline_subprocess(cfg, 3)
+            entry["cpu_ms"] = cpu["ms_per_step"] if cpu else None
+            entry["cpu_cores"] = cpu["cores"] if cpu else None
+        configs.append(entry)
+    line["configs"] = configs
     if rank == 0:
-        print(json.dumps({
-            "metric": "effective_binary_tops", "value": value, "unit": "TOPS", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "s8" if kernel_name == "tcgen05_i8" else "u32", "data": "synthetic",
-            "config": {"workload": L.name, "minibatch": L.mb, "images_per_gpu": mb,
-                       "kernel": kernel_name, "parallelism": "minibatch slices x%d" % world,
-                       "l2": "inputs larger than L2: %d rotating tensor sets of %.1f MB"
-                             % (sets, step_bytes / 1e6),
-                       "launch": "cuda graph replay, one graph per tensor set"
-                                 if graphs is not None else "plain calls"},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-            "gpu_launches": int(launches)}))
-    conv.close()
+        print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
@@ -466,11 +691,13 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    L = synth.CONFIGS[args.config]
     if args.impl == "reference":
-        run_reference(args, L, rank)
+        os.environ.setdefault("OMP_PROC_BIND", "close")  # read by libgomp when it is loaded
+        os.environ.setdefault("XNOR_NN_ISA", "2")
+        head = "B" if args.config == "all" else args.config
+        run_reference(args, head, synth.CONFIGS[head], rank)
     else:
-        run_ours(args, L, rank, world, local_rank)
+        run_ours(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":

@@ -53,7 +53,7 @@ typedef enum {
     xnor_nn_resource_bin_weights = 5,    /* sign-packed weights (device layout) */
     xnor_nn_resource_a = 6,              /* fp32 [MB][IH][IW]: mean |x| over channels */
     xnor_nn_resource_k = 7,              /* fp32 [MB][OH][OW]: box-filtered A / (KH*KW) */
-    xnor_nn_resource_operations_count = 8, /* per-resource device context of this library */
+    xnor_nn_resource_operations_count = 8, /* int32 [OH][OW]: IC * filter taps inside the image */
 
     xnor_nn_resource_number = 9
 } xnor_nn_resource_type_t;
@@ -121,7 +121,9 @@ xnor_nn_status_t xnor_nn_allocate_resources(const xnor_nn_convolution_t *c,
 void xnor_nn_free_resources(xnor_nn_resources_t res);
 
 /* Replaces upstream src/binarize_weights_float.cpp:3-25 (helper of the training backward pass,
- * host arrays): to[i] = (from[i] >= 0 ? 1 : -1) * mean(from). Runs on the host. */
+ * host arrays): to[i] = (from[i] >= 0 ? 1 : -1) * mean(from). With two host pointers it runs on
+ * the host, summing in index order; with two device pointers it runs on the GPU (default stream,
+ * waited for). One pointer of each kind is not supported. */
 void xnor_nn_binarize_weights_float(const xnor_nn_convolution_t *c, const float *from,
                                     float *to);
 

@@ -57,6 +57,13 @@ xnor_nn_b200_kernel_t xnor_nn_b200_kernel_of(const xnor_nn_convolution_t *c);
  * to the device once instead of twice, and the mean-|x| map is produced by the packing pass. */
 xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_resources_t res);
 
+/* The first of the two kernels xnor_nn_b200_forward runs, on its own: one pass over
+ * res[user_src] that packs the signs into res[bin_src] (binarize_data,
+ * src/bcast_binarize_data.cpp:43-73) and leaves the mean-|x| map in res[a] (the first loop of
+ * calculate_k, src/bcast_calculate_k.cpp:49-66). For callers that want to overlap the packing of
+ * one minibatch with other work, and for the benchmark, which times this kernel separately. */
+xnor_nn_status_t xnor_nn_b200_binarize(const xnor_nn_convolution_t *c, xnor_nn_resources_t res);
+
 /* Consecutive binary convolutions with no float tensor between them: layer i's results never
  * leave the chip as floats; the convolution kernel writes their signs straight into layer i+1's
  * packed input and their mean magnitude into its mean-|x| map, which is what layer i+1's

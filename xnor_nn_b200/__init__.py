@@ -78,6 +78,7 @@ def lib():
         L.xnor_nn_b200_binarize_weights_float.argtypes = [dp, C.c_void_p, C.c_void_p, C.c_void_p]
         L.xnor_nn_b200_kernel_of.argtypes = [dp]
         L.xnor_nn_b200_forward.argtypes = [dp, rp]
+        L.xnor_nn_b200_binarize.argtypes = [dp, rp]
         L.xnor_nn_b200_forward_chain.argtypes = [C.c_int, C.POINTER(dp), C.POINTER(rp)]
         L.xnor_nn_b200_forward_sums.argtypes = [dp, rp, C.c_void_p]
         L.xnor_nn_b200_read_resource.argtypes = [dp, rp, C.c_int, C.c_void_p, C.c_size_t]

@@ -713,6 +713,27 @@ xnor_nn_status_t xnor_nn_b200_forward(const xnor_nn_convolution_t *c, xnor_nn_re
     return xnor_nn_success;
 }
 
+xnor_nn_status_t xnor_nn_b200_binarize(const xnor_nn_convolution_t *c, xnor_nn_resources_t res) {
+    if (!c || !res || !res[xnor_nn_resource_user_src] || !res[xnor_nn_resource_bin_src] ||
+        !res[xnor_nn_resource_a])
+        return xnor_nn_error_invalid_input;
+    const Plan *p = plan_of(c);
+    ResCtx *x = find_ctx(res);
+    if (!p || !x) return xnor_nn_error_invalid_input;
+    if (!p->formats_ok) return xnor_nn_unimplemented;
+    DeviceGuard dg(x->device);
+    log_exec(*p, "binarize with mean-|x| map");
+    x->staged_a_valid = false;
+    const void *src = nullptr;
+    bool staged = false;
+    xnor_nn_status_t st = stage_in(x, 0, res[xnor_nn_resource_user_src], src_bytes(*p), &src, &staged);
+    if (st != xnor_nn_success) return st;
+    CU(launch_binarize_data(*p, (const float *)src, res[xnor_nn_resource_bin_src],
+                            (float *)res[xnor_nn_resource_a], x->stream));
+    if (staged) CU(cudaStreamSynchronize(x->stream));
+    return xnor_nn_success;
+}
+
 xnor_nn_status_t xnor_nn_b200_forward_chain(int layers, const xnor_nn_convolution_t *const *c,
                                             void **const *res) {
     if (layers < 1 || layers > 64 || !c || !res) return xnor_nn_error_invalid_input;

@@ -7,7 +7,7 @@
 // lanes of a warp read 32 neighbouring pixels of one channel plane, a full 128-byte line.
 #include "kernels.cuh"
 
-#include <cstdlib>
+#include <atomic>
 
 namespace xb200 {
 
@@ -303,13 +303,11 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
         // per thread outstanding does not need that many warps. Measured on conv4, minibatch 256:
         // the pass with the mean-|x| map 20.9 -> 19.1 us, and the convolution that follows starts
         // about 3 us earlier (whole step 65.5 -> 60.4 us).
-        static bool tuned[64] = {};
+        static std::atomic<bool> tuned[64];
         int dev = 0;
         cudaGetDevice(&dev);
-        if (!tuned[dev & 63]) {
-            tuned[dev & 63] = true;
-            int blocks = kResidentBlocks;
-            if (const char *e = getenv("XNOR_NN_B200_BIN_BLOCKS")) blocks = atoi(e);
+        if (!tuned[dev & 63].exchange(true, std::memory_order_acq_rel)) {
+            const int blocks = kResidentBlocks;
             cudaFuncAttributes fa;
             int smem_sm = 0;
             if (blocks > 0 &&

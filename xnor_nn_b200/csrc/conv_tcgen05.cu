@@ -466,7 +466,10 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- MMA issuer: kept lean, a single thread feeds the tensor pipe ----
+            // ---- MMA issuer: a single thread feeds the tensor pipe. The instructions of a stage
+            // (four tcgen05.mma, one tcgen05.commit) cost it about 350 cycles, so the loop
+            // carries nothing else: the next stage's barrier is tested before this stage's
+            // instructions are issued and looked at after them. ----
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -474,6 +477,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint32_t a_lo0 = ((stage0 >> 4) & 0x3FFF) | (1u << 16);
             const uint32_t b_lo0 = (((stage0 + g.a_bytes) >> 4) & 0x3FFF) | (1u << 16);
             const uint32_t stage_units = g.stage_bytes >> 4;
+            const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+            uint32_t ready = mbar_test(full0, 0);
+            uint32_t desc_off = 0;  // stage * stage_units
             for (int it = 0; ok && it < rounds; it++) {
                 const int b = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
@@ -483,22 +489,28 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
                 uint32_t accumulate = 0;
                 for (int ks = 0; ks < ksteps; ks++) {
-                    const uint32_t fbar = smem_u32(&ctl->full[stage]);
-                    if (!mbar_try_wait(fbar, phase)) {
-                        ok = mbar_wait(fbar, phase, abort_flag, g.error, 3, g.wait_ns);
-                        if (!ok) break;
+                    if (!ready) {
+                        const uint32_t fbar = full0 + 8u * (uint32_t)stage;
+                        if (!mbar_try_wait(fbar, phase)) {
+                            ok = mbar_wait(fbar, phase, abort_flag, g.error, 3, g.wait_ns);
+                            if (!ok) break;
+                        }
                     }
-                    fence_after();
-                    const uint64_t adesc = hi | (uint64_t)(a_lo0 + (uint32_t)stage * stage_units);
-                    const uint64_t bdesc = hi | (uint64_t)(b_lo0 + (uint32_t)stage * stage_units);
+                    const int next = stage == kStages - 1 ? 0 : stage + 1;
+                    const uint32_t next_phase = stage == kStages - 1 ? phase ^ 1u : phase;
+                    ready = mbar_test(full0 + 8u * (uint32_t)next, next_phase);
+                    const uint64_t adesc = hi | (uint64_t)(a_lo0 + desc_off);
+                    const uint64_t bdesc = hi | (uint64_t)(b_lo0 + desc_off);
 #pragma unroll
                     for (int k = 0; k < KK; k++) {
                         mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
                                   g.idesc, k == 0 ? accumulate : 1u);
                     }
                     accumulate = 1;
-                    commit(smem_u32(&ctl->empty[stage]));
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    commit(empty0 + 8u * (uint32_t)stage);
+                    desc_off = next == 0 ? 0u : desc_off + stage_units;
+                    stage = next;
+                    phase = next_phase;
                 }
                 if (ok && !(g.drop_commit && it == 0 && blockIdx.x == 0))
                     commit(smem_u32(&ctl->acc_full[b]));

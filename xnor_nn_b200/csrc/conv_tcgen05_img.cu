@@ -53,7 +53,8 @@ using namespace tc;
 constexpr int kFilters = 128;       // filters per tile = UMMA M = TMEM lanes
 constexpr int kTeam = 2;            // epilogue warps per TMEM lane quadrant (they split the columns)
 constexpr int kEpiWarps = 4 * kTeam;
-constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kProducerW = 2 + kEpiWarps;  // the warp that loads the weight tiles
+constexpr int kThreads = 32 * (kProducerW + 1);
 constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns
 constexpr int kMaxStages = 8;
 constexpr int kControlBytes = 2304;
@@ -86,16 +87,7 @@ struct ImgArgs {
     int bulk;                // whole-image tiles whose 32-filter blocks may leave as bulk stores
     unsigned long long wait_ns;
     int drop_commit;  // self-test: CTA 0 leaves out the commit that publishes its first tile
-#ifdef XB200_TRACE
-    long long *trace;  // development builds: clock64 stamps of CTA 0's roles
-#endif
 };
-
-#ifdef XB200_TRACE
-#define TRACE(slot) do { if (g.trace && blockIdx.x == 0) g.trace[slot] = clock64(); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#endif
 
 struct __align__(16) Control {
     unsigned long long full[kMaxStages];
@@ -175,7 +167,7 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; s++) {
-            mbar_init(smem_u32(&ctl->full[s]), 1);
+            mbar_init(smem_u32(&ctl->full[s]), 2);  // one arrival per producer
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
         for (int b = 0; b < 2; b++) {
@@ -208,62 +200,76 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
     const int ksteps = g.taps * g.chunks_per_tap;
     const uint32_t stage0 = smem_u32(stages);
 
-    if (warp == 0) {
+    if (warp == 0 || warp == kProducerW) {
         if (lane == 0) {
-            // ---- TMA producer ----
+            // ---- TMA producers: warp 0 loads the activation boxes, warp kProducerW the weight
+            // tiles. Every TMA instruction costs its issuing thread 80-90 cycles and the
+            // barrier operations 50-100 each (measured), so the two halves of a stage are
+            // issued by two threads; the ring slot's barrier counts both. The next slot's
+            // `empty` barrier is tested ahead, as in the MMA issuer. ----
             dependency_wait();
+            const bool weights = warp == kProducerW;
             int stage = 0;
             uint32_t phase = 0;
-            uint32_t armed = 0;  // bit s: stage s holds a load nobody is known to have consumed
-            uint32_t armed_parity = 0;
+            long issued = 0;  // stage loads issued by this thread
             bool ok = true;
+            const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+            const int last_stage = g.stages - 1;
+            uint32_t ready = 1;  // the ring starts empty
+            uint32_t sa = stage0 + (weights ? 0u : g.a_bytes);
             for (int it = 0; ok && it < rounds; it++) {
                 const Tile t = tile_of(g, (int)blockIdx.x + it * (int)gridDim.x);
                 const CUtensorMap *mx = t.half >= 0 ? &map_xh : &map_x;
-                const uint32_t tx = t.half >= 0 ? g.tx_half : g.tx_full;
+                const uint32_t tx = weights ? g.a_bytes
+                                            : (t.half >= 0 ? g.tx_half : g.tx_full) - g.a_bytes;
                 int wrow = t.mt * kFilters;  // row of the weight matrix: tap-major
-                int kh = 0, kw = 0, chunk = 0;
+                int y = t.r0 - g.ph, x = -g.pw, kw = 0, c = 0;
                 for (int ks = 0; ks < ksteps; ks++) {
-                    const uint32_t ebar = smem_u32(&ctl->empty[stage]);
-                    TRACE(4000 + (it * ksteps + ks) * 5 + 0);
-                    if (!mbar_try_wait(ebar, phase ^ 1)) {
-                        ok = mbar_wait(ebar, phase ^ 1, abort_flag, g.error, 1, g.wait_ns);
-                        if (!ok) break;
+                    if (!ready) {
+                        const uint32_t ebar = empty0 + 8u * (uint32_t)stage;
+                        if (!mbar_try_wait(ebar, phase ^ 1)) {
+                            ok = mbar_wait(ebar, phase ^ 1, abort_flag, g.error, 1, g.wait_ns);
+                            if (!ok) break;
+                        }
                     }
-                    TRACE(4000 + (it * ksteps + ks) * 5 + 1);
-                    armed &= ~(1u << stage);
-                    const uint32_t bar = smem_u32(&ctl->full[stage]);
-                    const uint32_t sa = stage0 + (uint32_t)stage * g.stage_bytes;
+                    const int next = stage == last_stage ? 0 : stage + 1;
+                    const uint32_t next_phase = stage == last_stage ? phase ^ 1u : phase;
+                    ready = issued + 1 < g.stages ? 1u
+                                                  : mbar_test(empty0 + 8u * (uint32_t)next,
+                                                              next_phase ^ 1u);
+                    const uint32_t bar = full0 + 8u * (uint32_t)stage;
                     mbar_expect_tx(bar, tx);
-                    TRACE(it * ksteps + ks);
-                    TRACE(4000 + (it * ksteps + ks) * 5 + 2);
-                    tma_load_2d(sa, &map_w, chunk * g.kchunk, wrow, bar);
-                    TRACE(4000 + (it * ksteps + ks) * 5 + 3);
-                    tma_load_4d(sa + g.a_bytes, mx, chunk * g.kchunk, kw - g.pw,
-                                t.r0 + kh - g.ph, t.n, bar);
-                    TRACE(4000 + (it * ksteps + ks) * 5 + 4);
-                    armed |= 1u << stage;
-                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-                    if (++stage == g.stages) { stage = 0; phase ^= 1; }
-                    if (++chunk == g.chunks_per_tap) {  // next filter tap
-                        chunk = 0;
+                    if (weights) tma_load_2d(sa, &map_w, c, wrow, bar);
+                    else tma_load_4d(sa, mx, c, x, y, t.n, bar);
+                    issued++;
+                    sa = next == 0 ? stage0 + (weights ? 0u : g.a_bytes) : sa + g.stage_bytes;
+                    stage = next;
+                    phase = next_phase;
+                    c += g.kchunk;
+                    if (c == g.chunks_per_tap * g.kchunk) {  // next filter tap
+                        c = 0;
                         wrow += g.ocp16;
-                        if (++kw == g.kw) { kw = 0; kh++; }
+                        x++;
+                        if (++kw == g.kw) { kw = 0; x = -g.pw; y++; }
                     }
                 }
             }
             if (!ok) {
                 // Something gave up. Loads already issued still land in this CTA's shared
                 // memory: wait for them (bounded) before the CTA may exit.
-                for (int s = 0; s < kMaxStages; s++)
-                    if (armed & (1u << s))
-                        mbar_wait_quiet(smem_u32(&ctl->full[s]), (armed_parity >> s) & 1u,
-                                        g.wait_ns);
+                for (long j = 0; j < g.stages && j < issued; j++) {
+                    const long gi = issued - 1 - j;
+                    mbar_wait_quiet(full0 + 8u * (uint32_t)(gi % g.stages),
+                                    (uint32_t)((gi / g.stages) & 1), g.wait_ns);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- MMA issuer: kept lean, a single thread feeds the tensor pipe ----
+            // ---- MMA issuer: a single thread feeds the tensor pipe. Per stage it spends about
+            // 25 cycles on each tcgen05.mma and 270 on the tcgen05.commit (measured), so the
+            // loop carries nothing else: the next stage's barrier is tested before this stage's
+            // instructions are issued and looked at after them. ----
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -271,6 +277,10 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
             const uint32_t a_lo0 = ((stage0 >> 4) & 0x3FFF) | (1u << 16);
             const uint32_t b_lo0 = (((stage0 + g.a_bytes) >> 4) & 0x3FFF) | (1u << 16);
             const uint32_t stage_units = g.stage_bytes >> 4;
+            const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+            const int last_stage = g.stages - 1;
+            uint32_t ready = mbar_test(full0, 0);
+            uint32_t desc_off = 0;  // stage * stage_units
             for (int it = 0; ok && it < rounds; it++) {
                 const int unit = (int)blockIdx.x + it * (int)gridDim.x;
                 const uint32_t idesc = unit >= g.whole ? g.idesc_half : g.idesc_full;
@@ -283,23 +293,27 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * 256);
                 uint32_t accumulate = 0;
                 for (int ks = 0; ks < ksteps; ks++) {
-                    const uint32_t fbar = smem_u32(&ctl->full[stage]);
-                    if (!mbar_try_wait(fbar, phase)) {
-                        ok = mbar_wait(fbar, phase, abort_flag, g.error, 3, g.wait_ns);
-                        if (!ok) break;
+                    if (!ready) {
+                        const uint32_t fbar = full0 + 8u * (uint32_t)stage;
+                        if (!mbar_try_wait(fbar, phase)) {
+                            ok = mbar_wait(fbar, phase, abort_flag, g.error, 3, g.wait_ns);
+                            if (!ok) break;
+                        }
                     }
-                    fence_after();
-                    TRACE(1000 + it * ksteps + ks);
-                    const uint64_t adesc = hi | (uint64_t)(a_lo0 + (uint32_t)stage * stage_units);
-                    const uint64_t bdesc = hi | (uint64_t)(b_lo0 + (uint32_t)stage * stage_units);
+                    const int next = stage == last_stage ? 0 : stage + 1;
+                    const uint32_t next_phase = stage == last_stage ? phase ^ 1u : phase;
+                    ready = mbar_test(full0 + 8u * (uint32_t)next, next_phase);
+                    const uint64_t adesc = hi | (uint64_t)(a_lo0 + desc_off);
+                    const uint64_t bdesc = hi | (uint64_t)(b_lo0 + desc_off);
 #pragma unroll
                     for (int k = 0; k < KK; k++)
                         mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
                                k == 0 ? accumulate : 1u);
                     accumulate = 1;
-                    commit(smem_u32(&ctl->empty[stage]));
-                    TRACE(2000 + it * ksteps + ks);
-                    if (++stage == g.stages) { stage = 0; phase ^= 1; }
+                    commit(empty0 + 8u * (uint32_t)stage);
+                    desc_off = next == 0 ? 0u : desc_off + stage_units;
+                    stage = next;
+                    phase = next_phase;
                 }
                 if (ok && !(g.drop_commit && it == 0 && blockIdx.x == 0))
                     commit(smem_u32(&ctl->acc_full[b]));
@@ -345,16 +359,13 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
                 }
             }
             bar_sync(1, 32 * kEpiWarps);
-            if (lane == 0 && cg == 0) TRACE(3000 + (it * 4 + e) * 5 + 0);
             if (live)
                 live = mbar_wait(smem_u32(&ctl->acc_full[b]), acc_phase, abort_flag, g.error, 4,
                                  g.wait_ns);
             live = __all_sync(0xffffffffu, live);  // tcgen05.ld needs the whole warp
             // my turn on the staging buffer: the warp that used it before has let go of it
             const long use = (long)it * 4 + e;
-            if (lane == 0 && cg == 0) TRACE(3000 + (it * 4 + e) * 5 + 1);
             if (staged && g.n_staging < 4 && use >= g.n_staging) bar_sync(2 + e, 32 * kTeam + 32);
-            if (lane == 0 && cg == 0) TRACE(3000 + (it * 4 + e) * 5 + 2);
 
             const int oc0 = t.mt * kFilters + q * 32, oc = oc0 + lane;
             const float al = (!g.sums && oc < g.oc) ? __ldg(g.alpha + oc) : 0.f;
@@ -385,7 +396,6 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
                         for (int j = 16; j < 32; j++) v[j] = 0;
                     }
                     wait_ld();
-                    if (lane == 0 && it == 0 && warp == 2) TRACE(9000 + (c0 >> 5) * 2);
                     if (c0 >= len) continue;
                     if (!g.sums) {
                         // Scale in registers first: K of the 32 pixels comes from shared memory
@@ -421,13 +431,11 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
                         for (int j = 0; j < 32; j++)
                             if (c0 + j < len) o[(long)j * g.oc] = v[j];
                     }
-                    if (lane == 0 && it == 0 && warp == 2) TRACE(9001 + (c0 >> 5) * 2);
                 }
                 // the accumulator is in registers / shared memory now: hand it back
                 fence_before();
                 mbar_arrive(smem_u32(&ctl->acc_empty[b]));
             }
-            if (lane == 0 && cg == 0) TRACE(3000 + (it * 4 + e) * 5 + 3);
             if (staged) {
                 fence_async_smem();
                 if (kTeam > 1) bar_sync(6 + q, 32 * kTeam);  // the team's rows are complete
@@ -463,7 +471,6 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
                 if (cg == 0 && g.n_staging < 4 && use + g.n_staging < uses)
                     bar_arrive(2 + (e + g.n_staging) % 4, 32 * kTeam + 32);
             }
-            if (lane == 0 && cg == 0) TRACE(3000 + (it * 4 + e) * 5 + 4);
         }
         bulk_wait_all();
     }
@@ -477,13 +484,6 @@ conv_tcgen05_img_kernel(const __grid_constant__ CUtensorMap map_w,
 }
 
 }  // namespace
-
-#ifdef XB200_TRACE
-long long *g_trace = nullptr;
-extern "C" __attribute__((visibility("default"))) void xnor_nn_b200_debug_trace(long long *p) {
-    g_trace = p;
-}
-#endif
 
 cudaError_t launch_conv_tcgen05_img(const Plan &p, const void *bin_src, const void *bin_w,
                                     const float *alpha, const float *k, const float *a,
@@ -541,9 +541,6 @@ cudaError_t launch_conv_tcgen05_img(const Plan &p, const void *bin_src, const vo
     g.bulk = contiguous && !(p.dst_nhwc && !sums) && ((uintptr_t)out & 15) == 0;
     g.wait_ns = test && test->wait_ns ? test->wait_ns : 2000000000ull;
     g.drop_commit = test ? test->drop_commit : 0;
-#ifdef XB200_TRACE
-    g.trace = g_trace;
-#endif
 
     const int kk = p.kchunk / 32;
     void (*kernel)(CUtensorMap, CUtensorMap, CUtensorMap, ImgArgs) =

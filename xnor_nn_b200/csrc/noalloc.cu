@@ -16,6 +16,7 @@
 //     every pixel the box filter reads is rewritten by the same call first;
 //   * the first call on a device looks the array's device address up (cudaGetSymbolAddress). Make
 //     that first call before any stream capture begins.
+#include <atomic>
 #include <cstdio>
 
 #include <cuda_runtime.h>
@@ -35,17 +36,19 @@ constexpr int kMaxDevices = 64;
 // kernels get comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) float g_noalloc_a[kNoAllocMaxPixels];
 
-float *g_scratch_of_device[kMaxDevices];  // filled on the first call per device
+std::atomic<float *> g_scratch_of_device[kMaxDevices];  // filled on the first call per device
 
 thread_local char t_noalloc_error[200] = "";
 
-bool device_pointer(const void *p) {
+// Device memory of GPU `dev` (or managed memory): what the kernels, which run on the current
+// device without peer access, can read and write.
+bool device_pointer(const void *p, int dev) {
     cudaPointerAttributes at;
     if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return false;
     }
-    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+    return at.type == cudaMemoryTypeManaged || (at.type == cudaMemoryTypeDevice && at.device == dev);
 }
 
 }  // namespace
@@ -68,17 +71,18 @@ xnor_nn_status_t xnor_nn_b200_calculate_k_noalloc(const xnor_nn_convolution_t *c
                  pixels, kNoAllocMaxPixels);
         return xnor_nn_error_invalid_input;
     }
-    if (!device_pointer(src_device) || !device_pointer(k_device)) {
-        snprintf(t_noalloc_error, sizeof t_noalloc_error,
-                 "calculate_k_noalloc: src and k must be device memory (nothing is staged)");
-        return xnor_nn_error_invalid_input;
-    }
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
         (void)cudaGetLastError();
         return xnor_nn_unimplemented;
     }
-    if (!g_scratch_of_device[dev]) {
+    if (!device_pointer(src_device, dev) || !device_pointer(k_device, dev)) {
+        snprintf(t_noalloc_error, sizeof t_noalloc_error,
+                 "calculate_k_noalloc: src and k must be memory of the current device "
+                 "(nothing is staged, no peer access is set up)");
+        return xnor_nn_error_invalid_input;
+    }
+    if (!g_scratch_of_device[dev].load(std::memory_order_acquire)) {
         // once per device, with that device current
         float *ptr = nullptr;
         const cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_noalloc_a);
@@ -88,9 +92,9 @@ xnor_nn_status_t xnor_nn_b200_calculate_k_noalloc(const xnor_nn_convolution_t *c
             (void)cudaGetLastError();
             return xnor_nn_unimplemented;
         }
-        g_scratch_of_device[dev] = ptr;
+        g_scratch_of_device[dev].store(ptr, std::memory_order_release);
     }
-    float *a = g_scratch_of_device[dev];
+    float *a = g_scratch_of_device[dev].load(std::memory_order_acquire);
     cudaStream_t s = (cudaStream_t)cuda_stream;
     cudaError_t e = launch_mean_abs(p, src_device, a, s);
     if (e == cudaSuccess) e = launch_box_filter(p, a, k_device, s);

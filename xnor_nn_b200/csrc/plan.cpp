@@ -131,10 +131,6 @@ void plan_image_rows(Plan *p) {
         n_staging = 1;
         stages = (budget - staging) / stage;
     }
-    if (const char *e = getenv("XNOR_NN_B200_DEV_STAGING")) {  // development override
-        n_staging = atoi(e);
-        stages = (budget - n_staging * staging) / stage;
-    }
     if (stages < 2) return;
     p->img_stages = (int)(stages > 8 ? 8 : stages);
     p->img_staging = n_staging;
