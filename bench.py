@@ -473,21 +473,25 @@ def measure_layer(xb, torch, args, cfg_name, kernel, rank, world, dist, probe, b
     ms_step = float(np.median(regions))
     value = binary_ops(L, L.mb) / (ms_step * 1e-3) / 1e12
 
-    # ---- the two kernels alone, same rotation (rank 0's slice is never empty) ---------------
+    # ---- the two kernels alone, same rotation; the slowest rank's figures are reported (with
+    # more GPUs than images some ranks, possibly rank 0, have nothing to do) -------------------
     if lay.conv is not None:
         lay.conv._set(xb.SLOT_USER_SRC, lay.d_src[0])
     n_k = max(20, min(steps, 200))
-    conv_ms = lay.timed(lay.conv_only, n_k) if lay.conv is not None else 0.0
-    bin_ms = lay.timed(lay.bin_only, n_k) if lay.conv is not None else 0.0
-    if rank != 0:  # only rank 0 reports; the others still take part in the collectives below
-        conv_ms = bin_ms = 1.0
-        lay.kernel_name = lay.kernel_name or "tcgen05_i8"
+    conv_ms = max_over_ranks(lay.timed(lay.conv_only, n_k) if lay.conv is not None else 0.0)
+    bin_ms = max_over_ranks(lay.timed(lay.bin_only, n_k) if lay.conv is not None else 0.0)
+    mb_max = int(max_over_ranks(float(mb)))
+    if dist is not None:
+        names = [None] * world
+        dist.all_gather_object(names, lay.kernel_name)
+        lay.kernel_name = next(n for n in names if n)
+    n_src_max = lay.n_src if mb == mb_max else mb_max * L.ic * L.ih * L.iw
     # compulsory bytes of the packing pass: 4 B per source element in, 1 B (tensor-core family)
     # or 1 bit (integer-pipe family) per element out, plus the mean-|x| map
     tc = (lay.kernel_name or "tcgen05").startswith("tcgen05")
-    bin_bytes = 4.0 * lay.n_src + (lay.n_src if tc else lay.n_src / 8.0) + 4.0 * mb * L.ih * L.iw
+    bin_bytes = 4.0 * n_src_max + (n_src_max if tc else n_src_max / 8.0) + 4.0 * mb_max * L.ih * L.iw
     pk, pk_kind = peaks()
-    conv_tops = binary_ops(L, mb) / (conv_ms * 1e-3) / 1e12
+    conv_tops = binary_ops(L, mb_max) / (conv_ms * 1e-3) / 1e12
     if tc:
         peak = probe.get("tcgen05_i8_tops") if probe else None
         peak_note = "tcgen05.mma kind::i8 ceiling measured in this run (pipe_probe)"
@@ -559,7 +563,7 @@ def measure_layer(xb, torch, args, cfg_name, kernel, rank, world, dist, probe, b
         "timed_regions": len(regions), "timed_ms": total,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "s8" if tc else "u32", "data": "synthetic",
-        "config": {"workload": L.name, "minibatch": L.mb, "images_per_gpu": mb,
+        "config": {"workload": L.name, "minibatch": L.mb, "images_per_gpu": mb_max,
                    "kernel": lay.kernel_name, "parallelism": "minibatch slices x%d" % world,
                    "l2": ("inputs larger than L2: %d rotating tensor sets of %.1f MB"
                           if lay.sets * lay.step_bytes > 2 * L2_BYTES else

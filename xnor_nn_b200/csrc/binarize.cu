@@ -127,14 +127,18 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 // pixel, which keeps upstream's summation order, while the other warps copy the byte tile out
 // as one coalesced 128-byte line per pixel. Seven blocks are resident per SM (72 registers per
 // thread, and the shared-memory carve-out is sized to match).
+//
+// TPER = channels per warp and chunk = loads per thread and chunk: 32 (chunks of 128 channels)
+// or 24 (chunks of 96), the latter for channel counts that are a multiple of 96 but not of 128
+// (AlexNet conv2), where a 128-channel chunk would leave a quarter of the threads without work.
+// Bytes past the last channel of a packed row are never written: they are zero from allocation.
 constexpr int TPX = 32;    // pixels per block
-constexpr int TCC = 128;   // channels per chunk
-constexpr int TLD = TCC + 4;
 constexpr int TWARPS = 4;
-constexpr int TPER = TCC / TWARPS;  // loads per thread and chunk
 
-template <bool WITH_A, bool WITH_PACK>
+template <bool WITH_A, bool WITH_PACK, int TPER>
 __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const BinArgs g) {
+    constexpr int TCC = TPER * TWARPS;  // channels per chunk
+    constexpr int TLD = TCC + 4;
     __shared__ float f_s[WITH_A ? TCC * TPX : 1];
     __shared__ __align__(16) uint8_t b_s[WITH_PACK ? TPX * TLD : 4];
     __shared__ long row_s[TPX];
@@ -153,7 +157,8 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
     const float *p = g.src + n * g.img_stride + r;
     if (warp == 0) row_s[lane] = live ? packed_row<kBytesFramed>(g, px) : -1;
 
-    const int c_end = WITH_PACK ? g.words * 4 : g.ic;  // channel extent walked
+    // channel extent walked: the channels, rounded up to whole 32-bit words of the packed row
+    const int c_end = WITH_PACK ? min(g.words * 4, (g.ic + 3) & ~3) : g.ic;
     float acc = 0.f;
     // Warp w owns the 32 consecutive channels [32w, 32w+32) of every chunk, so four of its sign
     // bytes make one 32-bit word of the packed row.
@@ -230,13 +235,13 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
         } else if (WITH_PACK) {
             // a warp writes one pixel per pass: 32 lanes x 4 bytes, one 128-byte line
             const int first = WITH_A ? warp - 1 : warp, step = WITH_A ? TWARPS - 1 : TWARPS;
-            const int nwords = min(TCC, c_end - c0) / 4;
+            const int nwords = (min(TCC, c_end - c0) + 3) / 4;
             constexpr int WPP = TCC / 4;   // 32-bit words per pixel and chunk
             constexpr int PPW = 32 / WPP;  // pixels a warp writes per pass
             const int half = lane / WPP, wl = lane % WPP;
             for (int pi = PPW * first + half; pi < TPX; pi += PPW * step) {
                 const long row = row_s[pi];
-                if (row >= 0 && wl < nwords)
+                if (row >= 0 && wl < nwords && half < PPW)
                     ((uint32_t *)g.out)[row * g.words + c0 / 4 + wl] =
                         *reinterpret_cast<const uint32_t *>(&b_s[pi * TLD + 4 * wl]);
             }
@@ -311,12 +316,14 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
             cudaFuncAttributes fa;
             int smem_sm = 0;
             if (blocks > 0 &&
-                cudaFuncGetAttributes(&fa, binarize_bytes_nchw_kernel<WITH_A, WITH_PACK>) == cudaSuccess &&
+                cudaFuncGetAttributes(&fa, binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>) == cudaSuccess &&
                 cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess &&
                 smem_sm > 0) {
                 long pct = (100L * blocks * ((long)fa.sharedSizeBytes + 1024) + smem_sm - 1) / smem_sm;
                 if (pct > 100) pct = 100;
-                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK>,
+                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>,
+                                     cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
+                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24>,
                                      cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
             }
             (void)cudaGetLastError();
@@ -325,8 +332,11 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
         // Launched with programmatic stream serialisation like the convolution: behind one of
         // this library's kernels (which trigger early) the blocks become resident while it
         // drains and wait in dependency_wait(); behind anything else nothing changes.
-        return launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK>,
-                                 dim3((unsigned)((g.n_px + TPX - 1) / TPX)), dim3(TWARPS * 32), 0,
+        const dim3 grid((unsigned)((g.n_px + TPX - 1) / TPX)), block(TWARPS * 32);
+        if (g.ic % 96 == 0 && g.ic % 128 != 0)
+            return launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24>, grid, block,
+                                     0, s, g);
+        return launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>, grid, block, 0,
                                  s, g);
     }
     switch (p.family) {
