@@ -507,6 +507,8 @@ def measure_layer(xb, torch, args, cfg_name, kernel, rank, world, dist, probe, b
                 "traffic": traffic["bytes"] if traffic else None,
                 "traffic_source": traffic.get("source") if traffic else None,
                 "peak_source": peak_note, "ms": conv_ms,
+                "timing": "launches issued back to back on one stream, CUDA events around the "
+                          "sequence, milliseconds per launch (includes what lies between launches)",
                 "frac_of_2x_bf16_%s" % pk_kind: (conv_tops / alt_peak) if alt_peak else None,
                 "binarize": {"kernel": "sign-pack with the mean-|x| map (the pass the step runs)",
                              "bound": "hbm", "achieved": bin_bytes / (bin_ms * 1e-3) / 1e9,

@@ -19,6 +19,8 @@ OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libxnor_nn.so")
 PROBE_SRC = os.path.join(CSRC, "probe", "pipe_probe.cu")
 PROBE = os.path.join(PKG, "pipe_probe")
+ISSUE_SRC = os.path.join(CSRC, "probe", "issue_probe.cu")
+ISSUE = os.path.join(PKG, "issue_probe")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -67,6 +69,10 @@ def build(force=False, verbose=False):
     if force or _stale(PROBE, [PROBE_SRC, os.path.abspath(__file__)]):
         subprocess.check_call([NVCC] + ARCH + ["-O3", "-std=c++17", "-lineinfo", "-ccbin",
                                                "/usr/bin/g++", "-o", PROBE, PROBE_SRC])
+    # ... and so is the probe of instruction issue costs (profiles/ quotes its output).
+    if force or _stale(ISSUE, [ISSUE_SRC, os.path.join(CSRC, "tc_ptx.cuh"), os.path.abspath(__file__)]):
+        subprocess.check_call([NVCC] + ARCH + ["-O3", "-std=c++17", "-lineinfo", "-ccbin",
+                                               "/usr/bin/g++", "-o", ISSUE, ISSUE_SRC])
     return LIB
 
 
