@@ -68,6 +68,10 @@ def parse():
     ap.add_argument("--chain", action="store_true",
                     help="time AlexNet conv3 -> conv4 -> conv5 layer by layer and as one chained "
                          "call (xnor_nn_b200_forward_chain), print one JSON line and exit")
+    ap.add_argument("--pcie", action="store_true",
+                    help="measure what the host delivers to the GPUs of this run: pinned "
+                         "host-to-device, device-to-host and both at once, all ranks together; "
+                         "print one JSON line and exit")
     ap.add_argument("--graph", action="store_true",
                     help="replay the step from CUDA graphs instead of calling the library")
     return ap.parse_args()
@@ -627,6 +631,56 @@ def chain_line(xb, torch, mb, reps):
         cv.close()
 
 
+def pcie_line(torch, dist, rank, world):
+    """Pinned-memory copy rates with every rank of the run copying at the same time: the floor
+    under the end-to-end figure, whose every step moves its slice up and its results down."""
+    mb = 64
+    h_up = torch.empty(mb << 20, dtype=torch.uint8).pin_memory()
+    h_dn = torch.empty(mb << 20, dtype=torch.uint8).pin_memory()
+    d_up = torch.empty(mb << 20, dtype=torch.uint8, device="cuda")
+    d_dn = torch.empty(mb << 20, dtype=torch.uint8, device="cuda")
+    s_up, s_dn = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def gbs(up, down, reps=8):
+        rates = []
+        for _ in range(3):
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                if up:
+                    with torch.cuda.stream(s_up):
+                        d_up.copy_(h_up, non_blocking=True)
+                if down:
+                    with torch.cuda.stream(s_dn):
+                        h_dn.copy_(d_dn, non_blocking=True)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            rates.append((up + down) * reps * (mb << 20) / dt / 1e9)
+        return float(np.median(rates))
+
+    mine = [gbs(1, 0), gbs(0, 1), gbs(1, 1)]
+    rows = [mine]
+    if dist is not None:
+        rows = [None] * world
+        dist.all_gather_object(rows, mine)
+    if rank == 0:
+        a = np.array(rows)
+        print(json.dumps({
+            "pcie": "pinned host memory, %d MB per copy, all %d ranks at once" % (mb, world),
+            "n_gpus": world, "unit": "GB/s",
+            "per_rank": {"h2d": a[:, 0].round(1).tolist(), "d2h": a[:, 1].round(1).tolist(),
+                         "both_directions": a[:, 2].round(1).tolist()},
+            "aggregate": {"h2d": float(a[:, 0].sum()), "d2h": float(a[:, 1].sum()),
+                          "both_directions": float(a[:, 2].sum())},
+            "slowest_rank": {"h2d": float(a[:, 0].min()), "d2h": float(a[:, 1].min()),
+                             "both_directions": float(a[:, 2].min())}}))
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import xnor_nn_b200 as xb
@@ -656,6 +710,11 @@ def run_ours(args, rank, world, local_rank):
         return
     if args.chain:
         chain_line(xb, torch, args.minibatch or 256, max(20, min(args.steps, 200)))
+        return
+    if args.pcie:
+        pcie_line(torch, dist, rank, world)
+        if dist is not None:
+            dist.destroy_process_group()
         return
     others = [] if args.only else [c for c in synth.CONFIGS if c != head]
     probe = pipe_probe() if rank == 0 and not args.no_probe else None
