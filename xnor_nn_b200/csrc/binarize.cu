@@ -135,7 +135,87 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 constexpr int TPX = 32;    // pixels per block
 constexpr int TWARPS = 4;
 
-template <bool WITH_A, bool WITH_PACK, int TPER>
+// One chunk of TCC channels whose values are in v: the |x|/IC tile and the sign-byte tile go to
+// shared memory; then warp 0 continues the per-pixel sum while the other warps write the packed
+// rows. `prefetch` runs between the two halves, after the first barrier (v is free by then).
+template <bool WITH_A, bool WITH_PACK, int TPER, typename Prefetch>
+__device__ __forceinline__ void bin_chunk(const BinArgs &g, const float (&v)[TPER], int c0, int c_end,
+                                          float *f_s, uint8_t *b_s, const long *row_s, float &acc,
+                                          Prefetch prefetch) {
+    constexpr int TCC = TPER * TWARPS;
+    constexpr int TLD = TCC + 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cw = TPER * warp;  // first channel of this warp inside a chunk
+    const bool full = c0 + TCC <= g.ic;  // no channel tail in this chunk
+    if (WITH_A) {
+#pragma unroll
+        for (int i = 0; i < TPER; i++) f_s[(cw + i) * TPX + lane] = __fmul_rn(fabsf(v[i]), g.inv_ic);
+    }
+    if (WITH_PACK) {
+        uint32_t *brow = reinterpret_cast<uint32_t *>(b_s + lane * TLD) + cw / 4;
+#pragma unroll
+        for (int j = 0; j < TPER / 4; j++) {
+            // sign bit set -> 0xFF (-1), clear -> 0x01 (+1): 0x01 ^ (sign * 0xFE) per byte
+            const uint32_t m = (__float_as_uint(v[4 * j]) >> 31) |
+                               ((__float_as_uint(v[4 * j + 1]) >> 31) << 8) |
+                               ((__float_as_uint(v[4 * j + 2]) >> 31) << 16) |
+                               ((__float_as_uint(v[4 * j + 3]) >> 31) << 24);
+            uint32_t word = 0x01010101u ^ (m * 0xFEu);
+            if (!full) {  // channels past the last one are zero bytes
+                const int left = g.ic - (c0 + cw + 4 * j);
+                word = left >= 4 ? word : left <= 0 ? 0u : (word & (0xFFFFFFFFu >> (8 * (4 - left))));
+            }
+            brow[j] = word;
+        }
+    }
+    __syncthreads();
+    prefetch();
+    if (WITH_A && warp == 0) {
+        const int nc = min(TCC, g.ic - c0);
+        if (nc == TCC) {
+#pragma unroll
+            for (int j0 = 0; j0 < TCC; j0 += 16) {
+                float t[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
+#pragma unroll
+                for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
+            }
+        } else {
+            // channel tail: same order, groups of 16 loads in flight while they fit
+            int j0 = 0;
+            for (; j0 + 16 <= nc; j0 += 16) {
+                float t[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
+#pragma unroll
+                for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
+            }
+            for (; j0 < nc; j0++) acc = __fadd_rn(acc, f_s[j0 * TPX + lane]);
+        }
+    } else if (WITH_PACK) {
+        // a warp writes one pixel per pass: 32 lanes x 4 bytes, one 128-byte line
+        const int first = WITH_A ? warp - 1 : warp, step = WITH_A ? TWARPS - 1 : TWARPS;
+        const int nwords = (min(TCC, c_end - c0) + 3) / 4;
+        constexpr int WPP = TCC / 4;   // 32-bit words per pixel and chunk
+        constexpr int PPW = 32 / WPP;  // pixels a warp writes per pass
+        const int half = lane / WPP, wl = lane % WPP;
+        for (int pi = PPW * first + half; pi < TPX; pi += PPW * step) {
+            const long row = row_s[pi];
+            if (row >= 0 && wl < nwords && half < PPW)
+                ((uint32_t *)g.out)[row * g.words + c0 / 4 + wl] =
+                    *reinterpret_cast<const uint32_t *>(&b_s[pi * TLD + 4 * wl]);
+        }
+    }
+    __syncthreads();
+}
+
+// NCH = 0: the streaming form, one chunk of loads in flight ahead of the chunk being consumed;
+// with seven blocks per SM that keeps HBM busy on grids of several blocks per SM. NCH > 0: all
+// loads of the block's (at most NCH) chunks are issued before anything is consumed, so a block
+// pays the memory latency once instead of once per chunk. That is the form for grids so small
+// that every block is resident at once and the kernel lasts as long as one block does.
+template <bool WITH_A, bool WITH_PACK, int TPER, int NCH>
 __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const BinArgs g) {
     constexpr int TCC = TPER * TWARPS;  // channels per chunk
     constexpr int TLD = TCC + 4;
@@ -160,93 +240,37 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
     // channel extent walked: the channels, rounded up to whole 32-bit words of the packed row
     const int c_end = WITH_PACK ? min(g.words * 4, (g.ic + 3) & ~3) : g.ic;
     float acc = 0.f;
-    // Warp w owns the 32 consecutive channels [32w, 32w+32) of every chunk, so four of its sign
-    // bytes make one 32-bit word of the packed row.
+    // Warp w owns the TPER consecutive channels [TPER w, TPER (w+1)) of every chunk, so four of
+    // its sign bytes make one 32-bit word of the packed row.
     const float *pw = p + (long)(TPER * warp) * g.hw;
     const int cw = TPER * warp;  // first channel of this warp inside a chunk
-    float v[TPER];
-    if (live && TCC <= g.ic) {
+    auto load_chunk = [&](float (&v)[TPER], int c0) {
+        const float *pn = pw + (long)c0 * g.hw;
+        if (live && c0 + TCC <= g.ic) {
 #pragma unroll
-        for (int i = 0; i < TPER; i++) v[i] = ld_stream(pw + (long)i * g.hw);
-    } else {
-#pragma unroll
-        for (int i = 0; i < TPER; i++)
-            v[i] = (live && cw + i < g.ic) ? ld_stream(pw + (long)i * g.hw) : 0.f;
-    }
-    for (int c0 = 0; c0 < c_end; c0 += TCC) {
-        const bool full = c0 + TCC <= g.ic;  // no channel tail in this chunk
-        if (WITH_A) {
+            for (int i = 0; i < TPER; i++) v[i] = ld_stream(pn + (long)i * g.hw);
+        } else {
 #pragma unroll
             for (int i = 0; i < TPER; i++)
-                f_s[(cw + i) * TPX + lane] = __fmul_rn(fabsf(v[i]), g.inv_ic);
+                v[i] = (live && c0 + cw + i < g.ic) ? ld_stream(pn + (long)i * g.hw) : 0.f;
         }
-        if (WITH_PACK) {
-            uint32_t *brow = reinterpret_cast<uint32_t *>(b_s + lane * TLD) + cw / 4;
+    };
+    if (NCH > 0) {
+        float v[NCH > 0 ? NCH : 1][TPER];
 #pragma unroll
-            for (int j = 0; j < TPER / 4; j++) {
-                // sign bit set -> 0xFF (-1), clear -> 0x01 (+1): 0x01 ^ (sign * 0xFE) per byte
-                const uint32_t m = (__float_as_uint(v[4 * j]) >> 31) |
-                                   ((__float_as_uint(v[4 * j + 1]) >> 31) << 8) |
-                                   ((__float_as_uint(v[4 * j + 2]) >> 31) << 16) |
-                                   ((__float_as_uint(v[4 * j + 3]) >> 31) << 24);
-                uint32_t word = 0x01010101u ^ (m * 0xFEu);
-                if (!full) {  // channels past the last one are zero bytes
-                    const int left = g.ic - (c0 + cw + 4 * j);
-                    word = left >= 4 ? word : left <= 0 ? 0u : (word & (0xFFFFFFFFu >> (8 * (4 - left))));
-                }
-                brow[j] = word;
-            }
-        }
-        __syncthreads();
-        if (c0 + TCC < c_end) {  // next chunk's loads fly while this one is consumed
-            const float *pn = pw + (long)(c0 + TCC) * g.hw;
-            if (live && c0 + 2 * TCC <= g.ic) {
+        for (int ci = 0; ci < NCH; ci++)
+            if (ci * TCC < c_end) load_chunk(v[ci], ci * TCC);
 #pragma unroll
-                for (int i = 0; i < TPER; i++) v[i] = ld_stream(pn + (long)i * g.hw);
-            } else {
-#pragma unroll
-                for (int i = 0; i < TPER; i++)
-                    v[i] = (live && c0 + TCC + cw + i < g.ic) ? ld_stream(pn + (long)i * g.hw) : 0.f;
-            }
-        }
-        if (WITH_A && warp == 0) {
-            const int nc = min(TCC, g.ic - c0);
-            if (nc == TCC) {
-#pragma unroll
-                for (int j0 = 0; j0 < TCC; j0 += 16) {
-                    float t[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
-                }
-            } else {
-                // channel tail: same order, groups of 16 loads in flight while they fit
-                int j0 = 0;
-                for (; j0 + 16 <= nc; j0 += 16) {
-                    float t[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
-                }
-                for (; j0 < nc; j0++) acc = __fadd_rn(acc, f_s[j0 * TPX + lane]);
-            }
-        } else if (WITH_PACK) {
-            // a warp writes one pixel per pass: 32 lanes x 4 bytes, one 128-byte line
-            const int first = WITH_A ? warp - 1 : warp, step = WITH_A ? TWARPS - 1 : TWARPS;
-            const int nwords = (min(TCC, c_end - c0) + 3) / 4;
-            constexpr int WPP = TCC / 4;   // 32-bit words per pixel and chunk
-            constexpr int PPW = 32 / WPP;  // pixels a warp writes per pass
-            const int half = lane / WPP, wl = lane % WPP;
-            for (int pi = PPW * first + half; pi < TPX; pi += PPW * step) {
-                const long row = row_s[pi];
-                if (row >= 0 && wl < nwords && half < PPW)
-                    ((uint32_t *)g.out)[row * g.words + c0 / 4 + wl] =
-                        *reinterpret_cast<const uint32_t *>(&b_s[pi * TLD + 4 * wl]);
-            }
-        }
-        __syncthreads();
+        for (int ci = 0; ci < NCH; ci++)
+            if (ci * TCC < c_end)
+                bin_chunk<WITH_A, WITH_PACK, TPER>(g, v[ci], ci * TCC, c_end, f_s, b_s, row_s, acc, [] {});
+    } else {
+        float v[TPER];
+        load_chunk(v, 0);
+        for (int c0 = 0; c0 < c_end; c0 += TCC)
+            bin_chunk<WITH_A, WITH_PACK, TPER>(g, v, c0, c_end, f_s, b_s, row_s, acc, [&] {
+                if (c0 + TCC < c_end) load_chunk(v, c0 + TCC);  // flies while this one is consumed
+            });
     }
     if (WITH_A && warp == 0 && live) g.a[px] = acc;
 }
@@ -294,6 +318,20 @@ BinArgs bin_args(const Plan &p, const float *src, void *out, float *a) {
     return g;
 }
 
+constexpr int kEagerChunks = 3;     // chunks whose loads the small-grid form issues up front
+
+static int sm_count_of(int dev) {
+    static std::atomic<int> cached[64];
+    int v = cached[dev & 63].load(std::memory_order_relaxed);
+    if (v > 0) return v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+        (void)cudaGetLastError();
+        v = 148;
+    }
+    cached[dev & 63].store(v, std::memory_order_relaxed);
+    return v;
+}
+
 constexpr int kResidentBlocks = 7;  // tiled kernel: blocks per SM the carve-out is sized for
 
 template <bool WITH_A, bool WITH_PACK>
@@ -316,14 +354,14 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
             cudaFuncAttributes fa;
             int smem_sm = 0;
             if (blocks > 0 &&
-                cudaFuncGetAttributes(&fa, binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>) == cudaSuccess &&
+                cudaFuncGetAttributes(&fa, binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32, 0>) == cudaSuccess &&
                 cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess &&
                 smem_sm > 0) {
                 long pct = (100L * blocks * ((long)fa.sharedSizeBytes + 1024) + smem_sm - 1) / smem_sm;
                 if (pct > 100) pct = 100;
-                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>,
+                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32, 0>,
                                      cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
-                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24>,
+                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24, 0>,
                                      cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
             }
             (void)cudaGetLastError();
@@ -333,11 +371,19 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
         // this library's kernels (which trigger early) the blocks become resident while it
         // drains and wait in dependency_wait(); behind anything else nothing changes.
         const dim3 grid((unsigned)((g.n_px + TPX - 1) / TPX)), block(TWARPS * 32);
-        if (g.ic % 96 == 0 && g.ic % 128 != 0)
-            return launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24>, grid, block,
-                                     0, s, g);
-        return launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>, grid, block, 0,
-                                 s, g);
+        const bool by96 = g.ic % 96 == 0 && g.ic % 128 != 0;
+        // every block resident at once (three per SM at the eager form's register count)
+        const bool small = grid.x <= 3u * (unsigned)sm_count_of(dev) &&
+                           g.ic <= kEagerChunks * (by96 ? 96 : 128);
+        if (by96)
+            return small ? launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24, kEagerChunks>,
+                                             grid, block, 0, s, 1, g)
+                         : launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24, 0>, grid,
+                                             block, 0, s, 1, g);
+        return small ? launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32, kEagerChunks>,
+                                         grid, block, 0, s, 1, g)
+                     : launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32, 0>, grid,
+                                         block, 0, s, 1, g);
     }
     switch (p.family) {
         case kPopc: binarize_kernel<kBitsDense, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;

@@ -12,15 +12,22 @@
 // Positions on the frame border are computed and dropped by the epilogue.
 //
 // One CTA per SM, persistent over (position tile, filter tile) pairs:
-//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, each CTA fetching its own tiles) into rings of
-//               shared-memory buffers; completion is counted on an mbarrier per buffer
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, each CTA fetching its own
+//               tiles) into a ring of shared-memory buffers; completion is counted on an
+//               mbarrier per buffer
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma.kind::i8 (M=128, N<=256,
 //               K=32 per instruction) into one of two accumulators in tensor memory, and
 //               tcgen05.commit hands buffers back / accumulators on
+//   warp 18     one lane is a second MMA issuer; the two take alternate ring buffers
 //   warps 2-17  epilogue: tcgen05.ld the accumulator (a warp owns 32 TMEM lanes = 32 positions
 //               and a share of the columns), scale by alpha[filter] * K[position] in upstream's
 //               order and store; runs under the next tile's MMAs thanks to the second
 //               accumulator
+//
+// Layers of more than one round of tiles run as clusters of two CTAs on tcgen05 cta_group::2:
+// the pair shares a tile of 256 positions x N filters, each CTA loads its own 128 positions and
+// half of the filter tile, the leader issues M = 256 instructions for both, and each CTA's
+// epilogue drains its own tensor memory.
 //
 // The epilogue has three forms: floats in NCHW (a warp store is one contiguous run of a filter
 // plane), floats in NHWC (a thread owns whole 32-byte sectors and writes them with 256-bit
@@ -33,6 +40,8 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstddef>
+#include <cstdlib>
 
 #include "kernels.cuh"
 #include "tc_ptx.cuh"
@@ -44,11 +53,11 @@ namespace {
 using namespace tc;
 
 constexpr int BM = 128;            // positions per tile = UMMA M = TMEM lanes
-constexpr int kStages = 4;
+constexpr int kMaxStages = 8;       // ring buffers: as many as fit, at most this
 constexpr int kEpiWarps = 16;       // epilogue warps: 4 TMEM lane quadrants x column groups
-constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kIssuer2Warp = 2 + kEpiWarps;  // the second MMA-issuing thread lives in a warp of its own
+constexpr int kThreads = 64 + 32 * kEpiWarps + 32;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns
-
 struct TcArgs {
     const float *alpha;
     const float *kmap;   // K per output pixel, or null: box-filter it from amap in the epilogue
@@ -75,6 +84,8 @@ struct TcArgs {
     int n_inner;          // 1: a CTA works through all filter tiles of a pixel tile in a row
     unsigned long long wait_ns;  // bound of every mbarrier wait
     int drop_commit;      // self-test: CTA 0 leaves out the commit that publishes its first tile
+    int issuers;          // threads that issue MMAs: 1, or 2 taking alternate pipeline stages
+    int n_stages;         // ring buffers in use
 };
 
 // ---- the kernel --------------------------------------------------------------------------------
@@ -83,49 +94,66 @@ constexpr int kAlphaSmem = 2048;  // filters whose alpha is staged in shared mem
 
 
 struct __align__(16) Control {
-    unsigned long long full[kStages];
-    unsigned long long empty[kStages];
+    unsigned long long full[kMaxStages];
+    unsigned long long empty[kMaxStages];
     unsigned long long acc_full[2];
     unsigned long long acc_empty[2];
-    unsigned long long drain;
+    unsigned long long started[2];  // two issuers: the tile's first MMA (which overwrites) is out
+    unsigned long long drain[2];
     uint32_t tmem_base;
     int abort_flag;
-    float alpha[kAlphaSmem];
+    alignas(16) float alpha[kAlphaSmem];  // read with 16-byte loads
     float fold[2][4][kEpiWarps / 4][32];  // chained layers: per-warp partial sums of |y|
 };
 constexpr int kControlBytes = (sizeof(Control) + 1023) / 1024 * 1024;
+static_assert(offsetof(Control, alpha) % 16 == 0, "alpha is read as float4");
 
-// Which tile a CTA works on in its it-th round. Default: tiles are dealt round-robin with the
-// filter tile as the fast index. n_inner: pixel tiles are dealt round-robin and a CTA walks all
-// filter tiles of its pixel tile back to back (so that per-pixel state can be carried across
-// them in registers).
-__device__ __forceinline__ int tile_rounds(const TcArgs &g) {
-    if (g.n_inner) {
-        const int mine = (g.m_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-        return mine > 0 ? mine * g.n_tiles : 0;
+// Which tile a CTA (PAIR: a pair of CTAs) works on in its it-th round. Default: tiles are dealt
+// round-robin with the filter tile as the fast index. n_inner: pixel tiles are dealt round-robin
+// and a CTA walks all filter tiles of its pixel tile back to back (so that per-pixel state can be
+// carried across them in registers). A pair's tile is two neighbouring pixel tiles, one per CTA.
+template <bool PAIR>
+struct Deal {
+    int unit, units, m_units;
+    __device__ __forceinline__ Deal(const TcArgs &g)
+        : unit(PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x),
+          units(PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x),
+          m_units(PAIR ? (g.m_tiles + 1) >> 1 : g.m_tiles) {}
+    __device__ __forceinline__ int rounds(const TcArgs &g) const {
+        if (g.n_inner) {
+            const int mine = (m_units - unit + units - 1) / units;
+            return mine > 0 ? mine * g.n_tiles : 0;
+        }
+        return (m_units * g.n_tiles - unit + units - 1) / units;
     }
-    const int total = g.m_tiles * g.n_tiles;
-    return (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-}
-__device__ __forceinline__ void tile_at(const TcArgs &g, int it, int &mt, int &nt) {
-    if (g.n_inner) {
-        const int r = it / g.n_tiles;
-        nt = it - r * g.n_tiles;
-        mt = (int)blockIdx.x + r * (int)gridDim.x;
-    } else {
-        const int tile = (int)blockIdx.x + it * (int)gridDim.x;
-        mt = tile / g.n_tiles;
-        nt = tile - mt * g.n_tiles;
+    // mt = pixel tile of this CTA
+    __device__ __forceinline__ void at(const TcArgs &g, int it, int &mt, int &nt) const {
+        int mu;
+        if (g.n_inner) {
+            const int r = it / g.n_tiles;
+            nt = it - r * g.n_tiles;
+            mu = unit + r * units;
+        } else {
+            const int tile = unit + it * units;
+            mu = tile / g.n_tiles;
+            nt = tile - mu * g.n_tiles;
+        }
+        mt = PAIR ? 2 * mu + (int)(blockIdx.x & 1) : mu;
     }
-}
+};
 
 // ---- epilogue role ---------------------------------------------------------------------------------
 // Warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); several warps share a quadrant and split
 // its columns between them.
+template <bool PAIR>
 __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uint32_t tmem_base,
                                               int warp, int lane, bool alpha_in_smem) {
     volatile int *abort_flag = &ctl->abort_flag;
-    const int rounds = tile_rounds(g);
+    const Deal<PAIR> deal(g);
+    const int rounds = deal.rounds(g);
+    // a pair's accumulators are handed back on the leader's barriers
+    const uint32_t acc_empty0 =
+        PAIR ? mapa(smem_u32(&ctl->acc_empty[0]), 0) : smem_u32(&ctl->acc_empty[0]);
     // Several warps share a quadrant and split its columns between them.
     const int quad = warp & 3;
     const int cgroup = (warp - 2) >> 2, cgroups = kEpiWarps / 4;
@@ -135,7 +163,7 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
     float run = 0.f;  // chained layers: running sum of |y| over the filter tiles of a pixel
     for (int it = 0; it < rounds; it++) {
         int mt, nt;
-        tile_at(g, it, mt, nt);
+        deal.at(g, it, mt, nt);
         const int b = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         const long q = (long)mt * BM + quad * 32 + lane;
@@ -361,12 +389,110 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
             }
         }
         fence_before();
-        mbar_arrive(smem_u32(&ctl->acc_empty[b]));
+        if (PAIR) {
+            // one arrival per warp: tcgen05.wait::ld is warp-wide, so every lane's reads are done
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8u * (uint32_t)b);
+        } else {
+            mbar_arrive(acc_empty0 + 8u * (uint32_t)b);
+        }
+    }
+}
+
+// ---- MMA issuer role -----------------------------------------------------------------------------
+// One thread feeds the tensor pipe; the instructions of a pipeline stage (KK tcgen05.mma and the
+// tcgen05.commit that hands the stage back) cost that thread more cycles than the pipe needs for
+// them unless N is 256. With two issuers the stages are dealt alternately (issuer i takes stages
+// i, i+2, ... of the running stage sequence, which continues across tiles), each commits its own
+// stages, and both commit to the accumulator's barrier (count 2) after their last stage of a
+// tile: a commit covers the MMAs of the committing thread only. The sum is over integers, so the
+// order in which the two threads' MMAs reach the pipe does not matter, except for the tile's
+// first instruction, which overwrites the accumulator: its issuer waits for the epilogue to have
+// drained the accumulator, and the other issuer waits for it (started[]).
+template <int KK, bool PAIR>
+__device__ __forceinline__ void mma_role(const TcArgs &g, Control *ctl, uint32_t tmem_base,
+                                         uint32_t stage0, int who) {
+    volatile int *abort_flag = &ctl->abort_flag;
+    const int rounds = Deal<PAIR>(g).rounds(g);
+    if (rounds == 0) return;
+    const int ksteps = g.taps * g.chunks_per_tap;  // >= g.issuers (the launcher sees to it)
+    const int n_iss = g.issuers;
+    const uint64_t hi = (uint64_t)g.desc_hi << 32;
+    const uint32_t a_lo0 = ((stage0 >> 4) & 0x3FFF) | (1u << 16);
+    const uint32_t b_lo0 = (((stage0 + g.a_bytes) >> 4) & 0x3FFF) | (1u << 16);
+    const uint32_t stage_units = g.stage_bytes >> 4;
+    const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+    const int n_stages = g.n_stages;  // >= g.issuers
+    int it = 0, ks = who, stage = who;
+    uint32_t phase = 0;
+    bool ok = true, entered = false;
+    for (;;) {
+        const int b = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!entered) {
+            if (ks == 0)
+                ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2,
+                               g.wait_ns);
+            else if (n_iss > 1)
+                ok = mbar_wait(smem_u32(&ctl->started[b]), acc_phase, abort_flag, g.error, 6,
+                               g.wait_ns);
+            if (!ok) break;
+            fence_after();
+            entered = true;
+        }
+        const uint32_t fbar = full0 + 8u * (uint32_t)stage;
+        if (!mbar_try_wait(fbar, phase)) {
+            ok = mbar_wait(fbar, phase, abort_flag, g.error, 3, g.wait_ns);
+            if (!ok) break;
+        }
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
+        const uint32_t desc_off = (uint32_t)stage * stage_units;
+        const uint64_t adesc = hi | (uint64_t)(a_lo0 + desc_off);
+        const uint64_t bdesc = hi | (uint64_t)(b_lo0 + desc_off);
+#pragma unroll
+        for (int k = 0; k < KK; k++) {
+            if (PAIR)
+                mma_i8_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), g.idesc,
+                            (k == 0 && ks == 0) ? 0u : 1u);
+            else
+                mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), g.idesc,
+                       (k == 0 && ks == 0) ? 0u : 1u);
+        }
+        if (PAIR) commit_pair(empty0 + 8u * (uint32_t)stage);  // frees the stage in both CTAs
+        else commit(empty0 + 8u * (uint32_t)stage);
+        if (n_iss > 1 && ks == 0) {
+            fence_before();
+            mbar_arrive(smem_u32(&ctl->started[b]));
+        }
+        stage += n_iss;
+        if (stage >= n_stages) { stage -= n_stages; phase ^= 1u; }
+        ks += n_iss;
+        if (ks >= ksteps) {  // this thread's share of the tile is issued
+            ks -= ksteps;
+            if (!(g.drop_commit && it == 0 && blockIdx.x == 0)) {
+                if (PAIR) commit_pair(smem_u32(&ctl->acc_full[b]));
+                else commit(smem_u32(&ctl->acc_full[b]));
+            }
+            entered = false;
+            if (++it >= rounds) break;
+        }
+    }
+    if (!ok) {
+        // Let every MMA this thread has issued finish before tensor memory is released.
+        if (PAIR) commit_pair(smem_u32(&ctl->drain[who]));
+        else commit(smem_u32(&ctl->drain[who]));
+        mbar_wait_quiet(smem_u32(&ctl->drain[who]), 0, g.wait_ns);
     }
 }
 
 // KK = tcgen05.mma instructions per pipeline stage (kchunk / 32).
-template <int KK>
+// PAIR: the grid is made of clusters of two CTAs that share tiles of 256 positions x N filters
+// (tcgen05 cta_group::2). Each CTA loads its own 128 positions and its half of the filter tile,
+// the leader (rank 0) issues one M = 256 instruction for both, and each CTA's epilogue drains its
+// own tensor memory. A stage is a third smaller per CTA that way (32 KB instead of 48 KB at
+// N = 256), which is what the kernel is short of: at one stage per 512 cycles a single CTA pulls
+// 94 B/clk from L2, four fifths of what the SM's port delivers.
+template <int KK, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_b, const TcArgs g) {
@@ -378,17 +504,20 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int *abort_flag = &ctl->abort_flag;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (int s = 0; s < g.n_stages; s++) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
         for (int b = 0; b < 2; b++) {
-            mbar_init(smem_u32(&ctl->acc_full[b]), 1);
-            mbar_init(smem_u32(&ctl->acc_empty[b]), 32 * kEpiWarps);
+            mbar_init(smem_u32(&ctl->acc_full[b]), (uint32_t)g.issuers);
+            // single CTA: one arrival per epilogue thread; pair: one per epilogue warp of both
+            mbar_init(smem_u32(&ctl->acc_empty[b]), PAIR ? 2 * kEpiWarps : 32 * kEpiWarps);
+            mbar_init(smem_u32(&ctl->started[b]), 1);
+            mbar_init(smem_u32(&ctl->drain[b]), 1);
         }
-        mbar_init(smem_u32(&ctl->drain), 1);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // the descriptors are launch parameters: fetch them while the predecessor still runs
@@ -396,6 +525,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     if (warp == 1) {
+        // Each CTA allocates all of its own tensor memory, so the accumulators sit at the same
+        // address in both CTAs of a pair.
         tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
     }
     // Everything above touched only this CTA's own shared and tensor memory and the launch
@@ -405,6 +536,10 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const bool alpha_in_smem = g.ocp16 <= kAlphaSmem;
     fence_before();
     __syncthreads();
+    if (PAIR) {  // the partner's barriers exist before anything is sent to them
+        cluster_arrive();
+        cluster_wait();
+    }
     fence_after();
     // Every CTA of this grid is resident from the start, so a dependent grid may be launched as
     // soon as all of them have got here: its CTAs move in as these exit (SMs with one tile fewer
@@ -412,7 +547,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     dependency_release();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    const int rounds = tile_rounds(g);
+    const Deal<PAIR> deal(g);
+    const int rounds = deal.rounds(g);
     const int ksteps = g.taps * g.chunks_per_tap;
     const uint32_t stage0 = smem_u32(stages);
 
@@ -425,11 +561,15 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             uint32_t armed = 0;  // bit s: stage s holds a load nobody is known to have consumed
             uint32_t armed_parity = 0;
             bool ok = true;
+            // a pair counts both CTAs' bytes on the leader's barrier
+            const uint32_t full_local = smem_u32(&ctl->full[0]);
+            const uint32_t full0 = PAIR && rank != 0 ? mapa(full_local, 0) : full_local;
+            const int b_rows = PAIR ? g.n_tile >> 1 : g.n_tile;  // filter rows this CTA loads
             for (int it = 0; ok && it < rounds; it++) {
                 int mt, nt;
-                tile_at(g, it, mt, nt);
+                deal.at(g, it, mt, nt);
                 int row = g.lead + mt * BM - g.ph * g.wp - g.pw;  // tap (0,0)
-                int brow = nt * g.n_tile;
+                int brow = nt * g.n_tile + (int)rank * b_rows;
                 int kw = 0, chunk = 0;
                 for (int ks = 0; ks < ksteps; ks++) {
                     const uint32_t ebar = smem_u32(&ctl->empty[stage]);
@@ -438,14 +578,20 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                         if (!ok) break;
                     }
                     armed &= ~(1u << stage);
-                    const uint32_t bar = smem_u32(&ctl->full[stage]);
+                    const uint32_t bar = full0 + 8u * (uint32_t)stage;
                     const uint32_t sa = stage0 + (uint32_t)stage * g.stage_bytes;
-                    mbar_expect_tx(bar, g.tx_bytes);
-                    tma_load_2d(sa, &map_a, chunk * g.kchunk, row, bar);
-                    tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
+                    if (PAIR) {
+                        if (rank == 0) mbar_expect_tx(bar, 2u * g.tx_bytes);  // bar is local here
+                        tma_load_2d_pair(sa, &map_a, chunk * g.kchunk, row, bar);
+                        tma_load_2d_pair(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
+                    } else {
+                        mbar_expect_tx(bar, g.tx_bytes);
+                        tma_load_2d(sa, &map_a, chunk * g.kchunk, row, bar);
+                        tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
+                    }
                     armed |= 1u << stage;
                     armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (++stage == g.n_stages) { stage = 0; phase ^= 1; }
                     if (++chunk == g.chunks_per_tap) {  // next filter tap
                         chunk = 0;
                         brow += g.ocp16;
@@ -454,73 +600,22 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     }
                 }
             }
-            if (!ok) {
+            if (!ok && rank == 0) {
                 // Something gave up. Loads already issued still land in this CTA's shared
-                // memory: wait for them (bounded) before the CTA may exit.
-                for (int s = 0; s < kStages; s++)
+                // memory: wait for them (bounded) before the CTA may exit. (The partner of a
+                // pair cannot wait on the leader's barrier; it stays until the leader has got
+                // through this and both have met at the cluster barrier below.)
+                for (int s = 0; s < g.n_stages; s++)
                     if (armed & (1u << s)) {
                         mbar_wait_quiet(smem_u32(&ctl->full[s]), (armed_parity >> s) & 1u,
                                         g.wait_ns);
                     }
             }
         }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- MMA issuer: a single thread feeds the tensor pipe. The instructions of a stage
-            // (four tcgen05.mma, one tcgen05.commit) cost it about 350 cycles, so the loop
-            // carries nothing else: the next stage's barrier is tested before this stage's
-            // instructions are issued and looked at after them. ----
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            const uint64_t hi = (uint64_t)g.desc_hi << 32;
-            const uint32_t a_lo0 = ((stage0 >> 4) & 0x3FFF) | (1u << 16);
-            const uint32_t b_lo0 = (((stage0 + g.a_bytes) >> 4) & 0x3FFF) | (1u << 16);
-            const uint32_t stage_units = g.stage_bytes >> 4;
-            const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
-            uint32_t ready = mbar_test(full0, 0);
-            uint32_t desc_off = 0;  // stage * stage_units
-            for (int it = 0; ok && it < rounds; it++) {
-                const int b = it & 1;
-                const uint32_t acc_phase = (it >> 1) & 1;
-                ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2, g.wait_ns);
-                if (!ok) break;
-                fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
-                uint32_t accumulate = 0;
-                for (int ks = 0; ks < ksteps; ks++) {
-                    if (!ready) {
-                        const uint32_t fbar = full0 + 8u * (uint32_t)stage;
-                        if (!mbar_try_wait(fbar, phase)) {
-                            ok = mbar_wait(fbar, phase, abort_flag, g.error, 3, g.wait_ns);
-                            if (!ok) break;
-                        }
-                    }
-                    const int next = stage == kStages - 1 ? 0 : stage + 1;
-                    const uint32_t next_phase = stage == kStages - 1 ? phase ^ 1u : phase;
-                    ready = mbar_test(full0 + 8u * (uint32_t)next, next_phase);
-                    const uint64_t adesc = hi | (uint64_t)(a_lo0 + desc_off);
-                    const uint64_t bdesc = hi | (uint64_t)(b_lo0 + desc_off);
-#pragma unroll
-                    for (int k = 0; k < KK; k++) {
-                        mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
-                                  g.idesc, k == 0 ? accumulate : 1u);
-                    }
-                    accumulate = 1;
-                    commit(empty0 + 8u * (uint32_t)stage);
-                    desc_off = next == 0 ? 0u : desc_off + stage_units;
-                    stage = next;
-                    phase = next_phase;
-                }
-                if (ok && !(g.drop_commit && it == 0 && blockIdx.x == 0))
-                    commit(smem_u32(&ctl->acc_full[b]));
-            }
-            if (!ok) {
-                // Let every MMA already issued finish before tensor memory is released.
-                commit(smem_u32(&ctl->drain));
-                mbar_wait_quiet(smem_u32(&ctl->drain), 0, g.wait_ns);
-            }
-        }
+    } else if (warp == 1 || warp == kIssuer2Warp) {
+        const int who = warp == 1 ? 0 : 1;
+        if (lane == 0 && who < g.issuers && rank == 0)
+            mma_role<KK, PAIR>(g, ctl, tmem_base, stage0, who);
         __syncwarp();
     } else {
         // ---- epilogue warps: stage alpha among themselves, then drain accumulators ----
@@ -530,11 +625,17 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 ctl->alpha[i] = i < g.oc ? __ldg(g.alpha + i) : 0.f;
             bar_sync(5, 32 * kEpiWarps);
         }
-        epilogue_role(g, ctl, tmem_base, warp, lane, alpha_in_smem);
+        epilogue_role<PAIR>(g, ctl, tmem_base, warp, lane, alpha_in_smem);
     }
 
     fence_before();
     __syncthreads();
+    if (PAIR) {
+        // Neither CTA leaves while the other may still read its shared or tensor memory or
+        // signal its barriers.
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp == 1) {
         fence_after();
         tmem_free(tmem_base, kTmemCols);
@@ -550,10 +651,28 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
                                 float *dst, int32_t *sums, int *error_word, cudaStream_t s,
                                 const ChainTarget *next, const ConvSelfTest *test) {
     if (p.q_total == 0) return cudaSuccess;
+    const int m_tiles = (int)((p.q_total + BM - 1) / BM);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    static std::atomic<int> sm_count[64], pair_count[64];
+    const int d = dev & 63;
+    int sms = sm_count[d].load(std::memory_order_relaxed);
+    if (!sms) {
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        sm_count[d].store(sms, std::memory_order_relaxed);
+    }
+    // CTA pairs when the layer is more than one round of tiles (measured on AlexNet conv4: 35.0
+    // against 36.9 us at 256 images, 24.3 against 24.9 at 128; with a single round the pair's
+    // longer hand-shakes cost more than its lighter loads save: 15.6 against 14.7 us at 64
+    // images). Floats or sums out only (the chained epilogue carries per-pixel state across the
+    // filter tiles of one CTA), and a filter tile that splits into two UMMA-sized halves.
+    const bool pair = !next && p.n_tile % 32 == 0 && m_tiles >= 2 &&
+                      (long)m_tiles * (p.ocp16 / p.n_tile) > sms;
+    const int b_rows = pair ? p.n_tile / 2 : p.n_tile;  // filter rows a CTA loads per stage
     CUtensorMap map_a, map_b;
     if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk, BM) ||
         !encode_bytes_2d(&map_b, bin_w, (uint64_t)p.kh * p.kw * p.ocp16, (uint64_t)p.icp,
-                         (uint32_t)p.kchunk, (uint32_t)p.n_tile))
+                         (uint32_t)p.kchunk, (uint32_t)b_rows))
         return cudaErrorNotSupported;
 
     TcArgs g;
@@ -561,7 +680,7 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.error = error_word;
     g.inv_khw = p.inv_khw; g.ih = p.ih; g.iw = p.iw; g.kh = p.kh;
     g.q_total = p.q_total;
-    g.m_tiles = (int)((p.q_total + BM - 1) / BM);
+    g.m_tiles = m_tiles;
     g.n_tiles = p.ocp16 / p.n_tile;
     g.n_tile = p.n_tile;
     g.kchunk = p.kchunk; g.chunks_per_tap = p.icp / p.kchunk; g.taps = p.kh * p.kw;
@@ -579,46 +698,71 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
         g.n_inner = 1;
     }
     // instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N and M encoded
+    // (M = 256 for a pair: 128 rows in each CTA)
     g.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.n_tile >> 3) << 17) |
-              ((uint32_t)(BM >> 4) << 24);
+              ((uint32_t)((pair ? 2 * BM : BM) >> 4) << 24);
     // matrix descriptor, upper half: stride between 8-row groups (8 * kchunk bytes, in 16-byte
     // units), descriptor version 1, swizzle mode
     const uint32_t sbo = (uint32_t)(8 * p.kchunk) >> 4;
     const uint32_t layout = p.kchunk == 128 ? 2u : p.kchunk == 64 ? 4u : 6u;
     g.desc_hi = sbo | (1u << 14) | (layout << 29);
     g.a_bytes = (uint32_t)(BM * p.kchunk);
-    g.tx_bytes = g.a_bytes + (uint32_t)(p.n_tile * p.kchunk);
+    g.tx_bytes = g.a_bytes + (uint32_t)(b_rows * p.kchunk);  // per CTA
     g.stage_bytes = (g.tx_bytes + 1023u) & ~1023u;
+    g.issuers = g.taps * g.chunks_per_tap < 2 ? 1 : 2;
+    // as many ring buffers as fit beside the control block
+    const size_t room = 227 * 1024 - 1024 - kControlBytes;
+    g.n_stages = (int)(room / g.stage_bytes);
+    if (g.n_stages > kMaxStages) g.n_stages = kMaxStages;
+    if (g.n_stages < 2) return cudaErrorNotSupported;
 
     const int kk = p.kchunk / 32;
-    void (*kernel)(CUtensorMap, CUtensorMap, TcArgs) = kk == 4   ? conv_tcgen05_kernel<4>
-                                                       : kk == 2 ? conv_tcgen05_kernel<2>
-                                                                 : conv_tcgen05_kernel<1>;
-    size_t smem = 1024 + kControlBytes + (size_t)kStages * g.stage_bytes;
+    void (*kernel)(CUtensorMap, CUtensorMap, TcArgs) =
+        pair ? (kk == 4   ? conv_tcgen05_kernel<4, true>
+                : kk == 2 ? conv_tcgen05_kernel<2, true>
+                          : conv_tcgen05_kernel<1, true>)
+             : (kk == 4   ? conv_tcgen05_kernel<4, false>
+                : kk == 2 ? conv_tcgen05_kernel<2, false>
+                          : conv_tcgen05_kernel<1, false>);
+    size_t smem = 1024 + kControlBytes + (size_t)g.n_stages * g.stage_bytes;
     // At least 120 KB of shared memory so that one CTA owns the SM and all 512 TMEM columns.
     if (smem < 120 * 1024) smem = 120 * 1024;
-    // per device and kernel, once: the opt-in to large dynamic shared memory and the SM count
-    int dev = 0;
-    cudaGetDevice(&dev);
-    static std::atomic<int> sm_count[64];
-    static std::atomic<bool> opted_in[64][3];
-    const int d = dev & 63;
-    std::atomic<bool> &done = opted_in[d][kk == 4 ? 0 : kk == 2 ? 1 : 2];
+    // per device and kernel, once: the opt-in to large dynamic shared memory, the SM count and
+    // the number of CTA pairs that can be resident together
+    static std::atomic<bool> opted_in[64][3][2];
+    std::atomic<bool> &done = opted_in[d][kk == 4 ? 0 : kk == 2 ? 1 : 2][pair ? 1 : 0];
     if (!done.load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(
             kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         done.store(true, std::memory_order_release);
     }
-    int sms = sm_count[d].load(std::memory_order_relaxed);
-    if (!sms) {
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        sm_count[d].store(sms, std::memory_order_relaxed);
+    note_launch();
+    if (pair) {
+        int pairs = pair_count[d].load(std::memory_order_relaxed);
+        if (!pairs) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * (sms / 2));
+            cfg.blockDim = dim3(kThreads);
+            cfg.dynamicSmemBytes = 227 * 1024 - 1024;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&pairs, kernel, &cfg) != cudaSuccess || pairs <= 0) {
+                (void)cudaGetLastError();
+                pairs = sms / 2;
+            }
+            pair_count[d].store(pairs, std::memory_order_relaxed);
+        }
+        const int tiles = ((m_tiles + 1) / 2) * g.n_tiles;
+        const int clusters = tiles < pairs ? tiles : pairs;
+        return launch_overlapped(kernel, dim3(2 * clusters), dim3(kThreads), smem, s, 2, map_a, map_b, g);
     }
     const int tiles = g.n_inner ? g.m_tiles : g.m_tiles * g.n_tiles;
     const int grid = tiles < sms ? tiles : sms;
-    note_launch();
-    return launch_overlapped(kernel, dim3(grid), dim3(kThreads), smem, s, map_a, map_b, g);
+    return launch_overlapped(kernel, dim3(grid), dim3(kThreads), smem, s, 1, map_a, map_b, g);
 }
 
 }  // namespace xb200

@@ -563,7 +563,7 @@ cudaError_t launch_conv_tcgen05_img(const Plan &p, const void *bin_src, const vo
         done.store(true, std::memory_order_release);
     }
     note_launch();
-    return launch_overlapped(kernel, dim3(p.img_grid), dim3(kThreads), smem, s, map_w, map_x,
+    return launch_overlapped(kernel, dim3(p.img_grid), dim3(kThreads), smem, s, 1, map_w, map_x,
                              map_xh, g);
 }
 

@@ -22,17 +22,24 @@ inline void note_launch(int n = 1) { g_kernel_launches.fetch_add(n, std::memory_
 // forward pass for the convolution, another 0.8 us for the binarizer in back-to-back passes).
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                     cudaStream_t s, Args... args) {
+                                     cudaStream_t s, int cluster, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (cluster > 1) {  // thread-block clusters of `cluster` CTAs along x
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = (unsigned)cluster;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
