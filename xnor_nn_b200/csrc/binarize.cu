@@ -8,6 +8,7 @@
 #include "kernels.cuh"
 
 #include <atomic>
+#include <cstdlib>
 
 namespace xb200 {
 
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 // one chunk ahead so that they are in flight while the previous chunk is consumed). |x|/IC goes to a float tile and the sign byte to a byte
 // tile in shared memory. Warp 0 then adds the float tile up channel by channel, one lane per
 // pixel, which keeps upstream's summation order, while the other warps copy the byte tile out
-// as one coalesced 128-byte line per pixel. Seven blocks are resident per SM (72 registers per
+// as one coalesced 128-byte line per pixel. Seven blocks are resident per SM (64 registers per
 // thread, and the shared-memory carve-out is sized to match).
 //
 // TPER = channels per warp and chunk = loads per thread and chunk: 32 (chunks of 128 channels)
@@ -210,12 +211,7 @@ __device__ __forceinline__ void bin_chunk(const BinArgs &g, const float (&v)[TPE
     __syncthreads();
 }
 
-// NCH = 0: the streaming form, one chunk of loads in flight ahead of the chunk being consumed;
-// with seven blocks per SM that keeps HBM busy on grids of several blocks per SM. NCH > 0: all
-// loads of the block's (at most NCH) chunks are issued before anything is consumed, so a block
-// pays the memory latency once instead of once per chunk. That is the form for grids so small
-// that every block is resident at once and the kernel lasts as long as one block does.
-template <bool WITH_A, bool WITH_PACK, int TPER, int NCH>
+template <bool WITH_A, bool WITH_PACK, int TPER>
 __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const BinArgs g) {
     constexpr int TCC = TPER * TWARPS;  // channels per chunk
     constexpr int TLD = TCC + 4;
@@ -255,23 +251,12 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
                 v[i] = (live && c0 + cw + i < g.ic) ? ld_stream(pn + (long)i * g.hw) : 0.f;
         }
     };
-    if (NCH > 0) {
-        float v[NCH > 0 ? NCH : 1][TPER];
-#pragma unroll
-        for (int ci = 0; ci < NCH; ci++)
-            if (ci * TCC < c_end) load_chunk(v[ci], ci * TCC);
-#pragma unroll
-        for (int ci = 0; ci < NCH; ci++)
-            if (ci * TCC < c_end)
-                bin_chunk<WITH_A, WITH_PACK, TPER>(g, v[ci], ci * TCC, c_end, f_s, b_s, row_s, acc, [] {});
-    } else {
-        float v[TPER];
-        load_chunk(v, 0);
-        for (int c0 = 0; c0 < c_end; c0 += TCC)
-            bin_chunk<WITH_A, WITH_PACK, TPER>(g, v, c0, c_end, f_s, b_s, row_s, acc, [&] {
-                if (c0 + TCC < c_end) load_chunk(v, c0 + TCC);  // flies while this one is consumed
-            });
-    }
+    float v[TPER];
+    load_chunk(v, 0);
+    for (int c0 = 0; c0 < c_end; c0 += TCC)
+        bin_chunk<WITH_A, WITH_PACK, TPER>(g, v, c0, c_end, f_s, b_s, row_s, acc, [&] {
+            if (c0 + TCC < c_end) load_chunk(v, c0 + TCC);  // flies while this one is consumed
+        });
     if (WITH_A && warp == 0 && live) g.a[px] = acc;
 }
 
@@ -318,20 +303,6 @@ BinArgs bin_args(const Plan &p, const float *src, void *out, float *a) {
     return g;
 }
 
-constexpr int kEagerChunks = 3;     // chunks whose loads the small-grid form issues up front
-
-static int sm_count_of(int dev) {
-    static std::atomic<int> cached[64];
-    int v = cached[dev & 63].load(std::memory_order_relaxed);
-    if (v > 0) return v;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
-        (void)cudaGetLastError();
-        v = 148;
-    }
-    cached[dev & 63].store(v, std::memory_order_relaxed);
-    return v;
-}
-
 constexpr int kResidentBlocks = 7;  // tiled kernel: blocks per SM the carve-out is sized for
 
 template <bool WITH_A, bool WITH_PACK>
@@ -354,14 +325,14 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
             cudaFuncAttributes fa;
             int smem_sm = 0;
             if (blocks > 0 &&
-                cudaFuncGetAttributes(&fa, binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32, 0>) == cudaSuccess &&
+                cudaFuncGetAttributes(&fa, binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>) == cudaSuccess &&
                 cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess &&
                 smem_sm > 0) {
                 long pct = (100L * blocks * ((long)fa.sharedSizeBytes + 1024) + smem_sm - 1) / smem_sm;
                 if (pct > 100) pct = 100;
-                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32, 0>,
+                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>,
                                      cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
-                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24, 0>,
+                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24>,
                                      cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
             }
             (void)cudaGetLastError();
@@ -371,19 +342,11 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
         // this library's kernels (which trigger early) the blocks become resident while it
         // drains and wait in dependency_wait(); behind anything else nothing changes.
         const dim3 grid((unsigned)((g.n_px + TPX - 1) / TPX)), block(TWARPS * 32);
-        const bool by96 = g.ic % 96 == 0 && g.ic % 128 != 0;
-        // every block resident at once (three per SM at the eager form's register count)
-        const bool small = grid.x <= 3u * (unsigned)sm_count_of(dev) &&
-                           g.ic <= kEagerChunks * (by96 ? 96 : 128);
-        if (by96)
-            return small ? launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24, kEagerChunks>,
-                                             grid, block, 0, s, 1, g)
-                         : launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24, 0>, grid,
-                                             block, 0, s, 1, g);
-        return small ? launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32, kEagerChunks>,
-                                         grid, block, 0, s, 1, g)
-                     : launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32, 0>, grid,
-                                         block, 0, s, 1, g);
+        if (g.ic % 96 == 0 && g.ic % 128 != 0)
+            return launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24>, grid, block,
+                                     0, s, 1, g);
+        return launch_overlapped(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>, grid, block, 0,
+                                 s, 1, g);
     }
     switch (p.family) {
         case kPopc: binarize_kernel<kBitsDense, WITH_A, WITH_PACK><<<blocks, threads, 0, s>>>(g); break;
