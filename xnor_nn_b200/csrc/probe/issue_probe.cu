@@ -4,6 +4,9 @@
 //   mma_group_cycles   cycles one thread needs for [4 x tcgen05.mma kind::i8, 1 x tcgen05.commit]
 //                      at several N: the tensor pipe needs N/2 cycles per instruction, the issue
 //                      side has a floor of its own (the commit dominates it)
+//   mma_group_cycles_two_issuers
+//                      the same number of groups dealt to two threads of different warps that
+//                      accumulate into the same tensor memory: cycles per group for the pair
 //   tma_stage_cycles   cycles per pipeline stage of a free-running TMA producer (one 128x128-byte
 //                      tile + one 4-D box of 169 rows, ring of four buffers), one SM and all SMs
 //   store_cycles       cycles per global store instruction of one warp, by access pattern
@@ -33,15 +36,18 @@ __device__ bool wait_bounded(uint32_t bar, uint32_t parity) {
 }
 
 // ---- [4 MMA + commit] ----------------------------------------------------------------------------
-__global__ void __launch_bounds__(64, 1) mma_groups(int n, int groups, long long *out, int *err) {
+__global__ void __launch_bounds__(96, 1)
+mma_groups(int n, int groups, int issuers, long long *out, int *err) {
     extern __shared__ uint8_t raw[];
     uint8_t *base = (uint8_t *)(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
-    __shared__ unsigned long long done, sink;
+    __shared__ unsigned long long done_s[2], sink_s[2];
     __shared__ uint32_t tm_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(smem_u32(&done), 1);
-        mbar_init(smem_u32(&sink), 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(smem_u32(&done_s[i]), 1);
+            mbar_init(smem_u32(&sink_s[i]), 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(smem_u32(&tm_s), 512);
@@ -49,8 +55,10 @@ __global__ void __launch_bounds__(64, 1) mma_groups(int n, int groups, long long
     __syncthreads();
     fence_after();
     const uint32_t tm = tm_s;
-    if (warp == 1 && lane == 0) {
-        const uint32_t sa = smem_u32(base), sb = sa + 16384;
+    if (warp >= 1 && warp - 1 < issuers && lane == 0) {
+        unsigned long long &done = done_s[warp - 1], &sink = sink_s[warp - 1];
+        groups /= issuers;
+        const uint32_t sa = smem_u32(base) + (uint32_t)(warp - 1) * 49152u, sb = sa + 16384;
         const uint64_t hi = (uint64_t)(64u | (1u << 14) | (2u << 29)) << 32;
         const uint64_t ad = hi | (uint64_t)(((sa >> 4) & 0x3FFF) | (1u << 16));
         const uint64_t bd = hi | (uint64_t)(((sb >> 4) & 0x3FFF) | (1u << 16));
@@ -63,7 +71,7 @@ __global__ void __launch_bounds__(64, 1) mma_groups(int n, int groups, long long
         }
         commit(smem_u32(&done));
         if (!wait_bounded(smem_u32(&done), 0)) *err = 1;
-        if (blockIdx.x == 0) out[0] = clock64() - t0;
+        if (blockIdx.x == 0) out[warp - 1] = clock64() - t0;
     }
     fence_before();
     __syncthreads();
@@ -183,15 +191,20 @@ int main() {
     cudaFuncSetAttribute(mma_groups, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     printf("\"mma_group_cycles\": {");
     const int ns[] = {64, 128, 176, 208, 256};
-    for (int i = 0; i < 5; i++) {
-        for (int rep = 0; rep < 2; rep++) {
-            mma_groups<<<sms, 64, 130 * 1024>>>(ns[i], 2048, out, err);
-            cudaDeviceSynchronize();
+    for (int issuers = 1; issuers <= 2; issuers++) {
+        if (issuers == 2) printf("\"mma_group_cycles_two_issuers\": {");
+        for (int i = 0; i < 5; i++) {
+            for (int rep = 0; rep < 2; rep++) {
+                cudaMemset(out, 0, 16);
+                mma_groups<<<sms, 96, 130 * 1024>>>(ns[i], 2048, issuers, out, err);
+                cudaDeviceSynchronize();
+            }
+            cudaMemcpy(h, out, 16, cudaMemcpyDeviceToHost);
+            const long long t = h[0] > h[1] ? h[0] : h[1];
+            printf("%s\"N=%d\": %.0f", i ? ", " : "", ns[i], t / 2048.0);
         }
-        cudaMemcpy(h, out, 8, cudaMemcpyDeviceToHost);
-        printf("%s\"N=%d\": %.0f", i ? ", " : "", ns[i], h[0] / 2048.0);
+        printf("}, ");
     }
-    printf("}, ");
 
     // TMA producer and bulk stores
     const int icp = 384, wp = 14, hp = 14, mb = 512;
