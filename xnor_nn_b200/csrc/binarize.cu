@@ -8,7 +8,6 @@
 #include "kernels.cuh"
 
 #include <atomic>
-#include <cstdlib>
 
 namespace xb200 {
 
@@ -126,7 +125,7 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 // one chunk ahead so that they are in flight while the previous chunk is consumed). |x|/IC goes to a float tile and the sign byte to a byte
 // tile in shared memory. Warp 0 then adds the float tile up channel by channel, one lane per
 // pixel, which keeps upstream's summation order, while the other warps copy the byte tile out
-// as one coalesced 128-byte line per pixel. Seven blocks are resident per SM (64 registers per
+// as one coalesced 128-byte line per pixel. Seven blocks are resident per SM (72 registers per
 // thread, and the shared-memory carve-out is sized to match).
 //
 // TPER = channels per warp and chunk = loads per thread and chunk: 32 (chunks of 128 channels)
@@ -135,81 +134,6 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 // Bytes past the last channel of a packed row are never written: they are zero from allocation.
 constexpr int TPX = 32;    // pixels per block
 constexpr int TWARPS = 4;
-
-// One chunk of TCC channels whose values are in v: the |x|/IC tile and the sign-byte tile go to
-// shared memory; then warp 0 continues the per-pixel sum while the other warps write the packed
-// rows. `prefetch` runs between the two halves, after the first barrier (v is free by then).
-template <bool WITH_A, bool WITH_PACK, int TPER, typename Prefetch>
-__device__ __forceinline__ void bin_chunk(const BinArgs &g, const float (&v)[TPER], int c0, int c_end,
-                                          float *f_s, uint8_t *b_s, const long *row_s, float &acc,
-                                          Prefetch prefetch) {
-    constexpr int TCC = TPER * TWARPS;
-    constexpr int TLD = TCC + 4;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int cw = TPER * warp;  // first channel of this warp inside a chunk
-    const bool full = c0 + TCC <= g.ic;  // no channel tail in this chunk
-    if (WITH_A) {
-#pragma unroll
-        for (int i = 0; i < TPER; i++) f_s[(cw + i) * TPX + lane] = __fmul_rn(fabsf(v[i]), g.inv_ic);
-    }
-    if (WITH_PACK) {
-        uint32_t *brow = reinterpret_cast<uint32_t *>(b_s + lane * TLD) + cw / 4;
-#pragma unroll
-        for (int j = 0; j < TPER / 4; j++) {
-            // sign bit set -> 0xFF (-1), clear -> 0x01 (+1): 0x01 ^ (sign * 0xFE) per byte
-            const uint32_t m = (__float_as_uint(v[4 * j]) >> 31) |
-                               ((__float_as_uint(v[4 * j + 1]) >> 31) << 8) |
-                               ((__float_as_uint(v[4 * j + 2]) >> 31) << 16) |
-                               ((__float_as_uint(v[4 * j + 3]) >> 31) << 24);
-            uint32_t word = 0x01010101u ^ (m * 0xFEu);
-            if (!full) {  // channels past the last one are zero bytes
-                const int left = g.ic - (c0 + cw + 4 * j);
-                word = left >= 4 ? word : left <= 0 ? 0u : (word & (0xFFFFFFFFu >> (8 * (4 - left))));
-            }
-            brow[j] = word;
-        }
-    }
-    __syncthreads();
-    prefetch();
-    if (WITH_A && warp == 0) {
-        const int nc = min(TCC, g.ic - c0);
-        if (nc == TCC) {
-#pragma unroll
-            for (int j0 = 0; j0 < TCC; j0 += 16) {
-                float t[16];
-#pragma unroll
-                for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
-#pragma unroll
-                for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
-            }
-        } else {
-            // channel tail: same order, groups of 16 loads in flight while they fit
-            int j0 = 0;
-            for (; j0 + 16 <= nc; j0 += 16) {
-                float t[16];
-#pragma unroll
-                for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
-#pragma unroll
-                for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
-            }
-            for (; j0 < nc; j0++) acc = __fadd_rn(acc, f_s[j0 * TPX + lane]);
-        }
-    } else if (WITH_PACK) {
-        // a warp writes one pixel per pass: 32 lanes x 4 bytes, one 128-byte line
-        const int first = WITH_A ? warp - 1 : warp, step = WITH_A ? TWARPS - 1 : TWARPS;
-        const int nwords = (min(TCC, c_end - c0) + 3) / 4;
-        constexpr int WPP = TCC / 4;   // 32-bit words per pixel and chunk
-        constexpr int PPW = 32 / WPP;  // pixels a warp writes per pass
-        const int half = lane / WPP, wl = lane % WPP;
-        for (int pi = PPW * first + half; pi < TPX; pi += PPW * step) {
-            const long row = row_s[pi];
-            if (row >= 0 && wl < nwords && half < PPW)
-                ((uint32_t *)g.out)[row * g.words + c0 / 4 + wl] =
-                    *reinterpret_cast<const uint32_t *>(&b_s[pi * TLD + 4 * wl]);
-        }
-    }
-    __syncthreads();
-}
 
 template <bool WITH_A, bool WITH_PACK, int TPER>
 __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const BinArgs g) {
@@ -236,27 +160,94 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
     // channel extent walked: the channels, rounded up to whole 32-bit words of the packed row
     const int c_end = WITH_PACK ? min(g.words * 4, (g.ic + 3) & ~3) : g.ic;
     float acc = 0.f;
-    // Warp w owns the TPER consecutive channels [TPER w, TPER (w+1)) of every chunk, so four of
-    // its sign bytes make one 32-bit word of the packed row.
+    // Warp w owns the 32 consecutive channels [32w, 32w+32) of every chunk, so four of its sign
+    // bytes make one 32-bit word of the packed row.
     const float *pw = p + (long)(TPER * warp) * g.hw;
     const int cw = TPER * warp;  // first channel of this warp inside a chunk
-    auto load_chunk = [&](float (&v)[TPER], int c0) {
-        const float *pn = pw + (long)c0 * g.hw;
-        if (live && c0 + TCC <= g.ic) {
+    float v[TPER];
+    if (live && TCC <= g.ic) {
 #pragma unroll
-            for (int i = 0; i < TPER; i++) v[i] = ld_stream(pn + (long)i * g.hw);
-        } else {
+        for (int i = 0; i < TPER; i++) v[i] = ld_stream(pw + (long)i * g.hw);
+    } else {
+#pragma unroll
+        for (int i = 0; i < TPER; i++)
+            v[i] = (live && cw + i < g.ic) ? ld_stream(pw + (long)i * g.hw) : 0.f;
+    }
+    for (int c0 = 0; c0 < c_end; c0 += TCC) {
+        const bool full = c0 + TCC <= g.ic;  // no channel tail in this chunk
+        if (WITH_A) {
 #pragma unroll
             for (int i = 0; i < TPER; i++)
-                v[i] = (live && c0 + cw + i < g.ic) ? ld_stream(pn + (long)i * g.hw) : 0.f;
+                f_s[(cw + i) * TPX + lane] = __fmul_rn(fabsf(v[i]), g.inv_ic);
         }
-    };
-    float v[TPER];
-    load_chunk(v, 0);
-    for (int c0 = 0; c0 < c_end; c0 += TCC)
-        bin_chunk<WITH_A, WITH_PACK, TPER>(g, v, c0, c_end, f_s, b_s, row_s, acc, [&] {
-            if (c0 + TCC < c_end) load_chunk(v, c0 + TCC);  // flies while this one is consumed
-        });
+        if (WITH_PACK) {
+            uint32_t *brow = reinterpret_cast<uint32_t *>(b_s + lane * TLD) + cw / 4;
+#pragma unroll
+            for (int j = 0; j < TPER / 4; j++) {
+                // sign bit set -> 0xFF (-1), clear -> 0x01 (+1): 0x01 ^ (sign * 0xFE) per byte
+                const uint32_t m = (__float_as_uint(v[4 * j]) >> 31) |
+                                   ((__float_as_uint(v[4 * j + 1]) >> 31) << 8) |
+                                   ((__float_as_uint(v[4 * j + 2]) >> 31) << 16) |
+                                   ((__float_as_uint(v[4 * j + 3]) >> 31) << 24);
+                uint32_t word = 0x01010101u ^ (m * 0xFEu);
+                if (!full) {  // channels past the last one are zero bytes
+                    const int left = g.ic - (c0 + cw + 4 * j);
+                    word = left >= 4 ? word : left <= 0 ? 0u : (word & (0xFFFFFFFFu >> (8 * (4 - left))));
+                }
+                brow[j] = word;
+            }
+        }
+        __syncthreads();
+        if (c0 + TCC < c_end) {  // next chunk's loads fly while this one is consumed
+            const float *pn = pw + (long)(c0 + TCC) * g.hw;
+            if (live && c0 + 2 * TCC <= g.ic) {
+#pragma unroll
+                for (int i = 0; i < TPER; i++) v[i] = ld_stream(pn + (long)i * g.hw);
+            } else {
+#pragma unroll
+                for (int i = 0; i < TPER; i++)
+                    v[i] = (live && c0 + TCC + cw + i < g.ic) ? ld_stream(pn + (long)i * g.hw) : 0.f;
+            }
+        }
+        if (WITH_A && warp == 0) {
+            const int nc = min(TCC, g.ic - c0);
+            if (nc == TCC) {
+#pragma unroll
+                for (int j0 = 0; j0 < TCC; j0 += 16) {
+                    float t[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
+                }
+            } else {
+                // channel tail: same order, groups of 16 loads in flight while they fit
+                int j0 = 0;
+                for (; j0 + 16 <= nc; j0 += 16) {
+                    float t[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
+                }
+                for (; j0 < nc; j0++) acc = __fadd_rn(acc, f_s[j0 * TPX + lane]);
+            }
+        } else if (WITH_PACK) {
+            // a warp writes one pixel per pass: 32 lanes x 4 bytes, one 128-byte line
+            const int first = WITH_A ? warp - 1 : warp, step = WITH_A ? TWARPS - 1 : TWARPS;
+            const int nwords = (min(TCC, c_end - c0) + 3) / 4;
+            constexpr int WPP = TCC / 4;   // 32-bit words per pixel and chunk
+            constexpr int PPW = 32 / WPP;  // pixels a warp writes per pass
+            const int half = lane / WPP, wl = lane % WPP;
+            for (int pi = PPW * first + half; pi < TPX; pi += PPW * step) {
+                const long row = row_s[pi];
+                if (row >= 0 && wl < nwords && half < PPW)
+                    ((uint32_t *)g.out)[row * g.words + c0 / 4 + wl] =
+                        *reinterpret_cast<const uint32_t *>(&b_s[pi * TLD + 4 * wl]);
+            }
+        }
+        __syncthreads();
+    }
     if (WITH_A && warp == 0 && live) g.a[px] = acc;
 }
 
