@@ -5,6 +5,7 @@ A case is (name, dict(mb, oc, ic, ih, iw, kh, kw, sh, sw, ph, pw), fill, formats
 formats = (src_nhwc, w_hwio, dst_nhwc). Inputs are always generated as NCHW / OIHW and permuted
 to the requested format, so a case means the same tensor in every layout.
 """
+import hashlib
 import zlib
 
 import numpy as np
@@ -56,6 +57,12 @@ SHAPE_CASES = [
     # last round, which the image-row kernel cuts into half tiles
     _c("split_tail_152_tiles", 38, 512, 8, 4, 4, 3, 3, ph=1, pw=1),
     _c("three_rounds_450_tiles", 150, 384, 8, 2, 2, 3, 3, ph=1, pw=1),
+    # more position tiles than SMs: the position-tile kernel runs them on CTA pairs. 151 tiles (an
+    # odd count: the last pair's second CTA owns no position at all, and 76 pair tiles are two
+    # rounds for two of the 74 pairs); two filter tiles of 192 with an odd number of position
+    # tiles; an NHWC result
+    _c("pairs_151_tiles", 2140, 32, 40, 2, 2, 3, 3, ph=1, pw=1),
+    _c("pairs_two_filter_tiles_of_192", 1060, 384, 8, 2, 2, 3, 3, ph=1, pw=1),
 ]
 
 # Tensor formats other than NCHW/OIHW/NCHW
@@ -68,6 +75,7 @@ FORMAT_CASES = [
     # aligned (13 filters): the narrower store paths of the tensor-core epilogue
     _c("fmt_nhwc_dst_oc20", 2, 20, 37, 6, 7, 3, 3, ph=1, pw=1, fmt=(0, 0, 1)),
     _c("fmt_nhwc_dst_oc13", 2, 13, 37, 6, 7, 3, 3, ph=1, pw=1, fmt=(0, 0, 1)),
+    _c("fmt_nhwc_dst_pairs", 2140, 32, 8, 2, 2, 3, 3, ph=1, pw=1, fmt=(0, 0, 1)),
 ]
 
 ALL_CASES = TAIL_CASES + SHAPE_CASES + FORMAT_CASES
@@ -102,3 +110,15 @@ def oracle_shape(case):
     _, d, _, fmt = case
     return Shape.make(d["mb"], d["oc"], d["ic"], d["ih"], d["iw"], d["kh"], d["kw"], d["sh"],
                       d["sw"], d["ph"], d["pw"], fmt[0], fmt[1], fmt[2])
+
+
+def golden_sums_match(golden, name, sums):
+    """Integer sums against the fixture, which holds them in full or, for the largest cases, as
+    the SHA-256 of their int16 form."""
+    if name + "/sums" in golden.files:
+        return np.array_equal(sums, golden[name + "/sums"].astype(np.int32))
+    s16 = np.asarray(sums).astype(np.int16)
+    if not np.array_equal(s16.astype(np.int32), np.asarray(sums).astype(np.int32)):
+        return False
+    digest = np.frombuffer(hashlib.sha256(s16.tobytes()).digest(), np.uint8)
+    return np.array_equal(digest, golden[name + "/sums_sha256"])
