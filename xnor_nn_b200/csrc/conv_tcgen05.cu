@@ -86,6 +86,8 @@ struct TcArgs {
     int drop_commit;      // self-test: CTA 0 leaves out the commit that publishes its first tile
     int issuers;          // threads that issue MMAs: 1, or 2 taking alternate pipeline stages
     int n_stages;         // ring buffers in use
+    int kk_last;          // MMAs of a tap's last channel chunk: its 32-channel slices that hold
+                          // channels at all (the chunk is padded with zero bytes to kchunk)
 };
 
 // ---- the kernel --------------------------------------------------------------------------------
@@ -424,6 +426,9 @@ __device__ __forceinline__ void mma_role(const TcArgs &g, Control *ctl, uint32_t
     const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
     const int n_stages = g.n_stages;  // >= g.issuers
     int it = 0, ks = who, stage = who;
+    // position of this thread's current stage among the chunks of its tap
+    int chunk = who % g.chunks_per_tap;
+    const int chunk_step = n_iss % g.chunks_per_tap;
     uint32_t phase = 0;
     bool ok = true, entered = false;
     for (;;) {
@@ -449,14 +454,18 @@ __device__ __forceinline__ void mma_role(const TcArgs &g, Control *ctl, uint32_t
         const uint32_t desc_off = (uint32_t)stage * stage_units;
         const uint64_t adesc = hi | (uint64_t)(a_lo0 + desc_off);
         const uint64_t bdesc = hi | (uint64_t)(b_lo0 + desc_off);
+        // slices of zero padding behind the last channel are not multiplied
+        const int kk = chunk == g.chunks_per_tap - 1 ? g.kk_last : KK;
 #pragma unroll
         for (int k = 0; k < KK; k++) {
-            if (PAIR)
-                mma_i8_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), g.idesc,
-                            (k == 0 && ks == 0) ? 0u : 1u);
-            else
-                mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), g.idesc,
-                       (k == 0 && ks == 0) ? 0u : 1u);
+            if (k < kk) {
+                if (PAIR)
+                    mma_i8_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
+                                g.idesc, (k == 0 && ks == 0) ? 0u : 1u);
+                else
+                    mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), g.idesc,
+                           (k == 0 && ks == 0) ? 0u : 1u);
+            }
         }
         if (PAIR) commit_pair(empty0 + 8u * (uint32_t)stage);  // frees the stage in both CTAs
         else commit(empty0 + 8u * (uint32_t)stage);
@@ -466,6 +475,8 @@ __device__ __forceinline__ void mma_role(const TcArgs &g, Control *ctl, uint32_t
         }
         stage += n_iss;
         if (stage >= n_stages) { stage -= n_stages; phase ^= 1u; }
+        chunk += chunk_step;
+        if (chunk >= g.chunks_per_tap) chunk -= g.chunks_per_tap;
         ks += n_iss;
         if (ks >= ksteps) {  // this thread's share of the tile is issued
             ks -= ksteps;
@@ -710,6 +721,7 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.tx_bytes = g.a_bytes + (uint32_t)(b_rows * p.kchunk);  // per CTA
     g.stage_bytes = (g.tx_bytes + 1023u) & ~1023u;
     g.issuers = g.taps * g.chunks_per_tap < 2 ? 1 : 2;
+    g.kk_last = (p.ic - (g.chunks_per_tap - 1) * p.kchunk + 31) / 32;
     // as many ring buffers as fit beside the control block
     const size_t room = 227 * 1024 - 1024 - kControlBytes;
     g.n_stages = (int)(room / g.stage_bytes);
