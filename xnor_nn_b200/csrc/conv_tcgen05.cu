@@ -56,8 +56,7 @@ constexpr int BM = 128;            // positions per tile = UMMA M = TMEM lanes
 constexpr int kMaxStages = 8;       // ring buffers: as many as fit, at most this
 constexpr int kEpiWarps = 16;       // epilogue warps: 4 TMEM lane quadrants x column groups
 constexpr int kIssuer2Warp = 2 + kEpiWarps;  // the second MMA-issuing thread lives in a warp of its own
-constexpr int kProducer2Warp = kIssuer2Warp + 1;  // and so does the second TMA producer
-constexpr int kThreads = 64 + 32 * kEpiWarps + 64;
+constexpr int kThreads = 64 + 32 * kEpiWarps + 32;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns
 struct TcArgs {
     const float *alpha;
@@ -564,96 +563,55 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int ksteps = g.taps * g.chunks_per_tap;
     const uint32_t stage0 = smem_u32(stages);
 
-    if (warp == 0 || warp == kProducer2Warp) {
+    if (warp == 0) {
         if (lane == 0) {
-            // ---- TMA producers. A stage costs its producer about 450 cycles of issue (a look at
-            // the slot's barrier 100-200, the byte count 20, two TMA instructions 83 each, the
-            // walk over taps and slots), which is more than the tensor pipe needs for a stage of
-            // a narrow tile and too close to what it needs for a wide one once the epilogue's
-            // stores slow everything down. So two threads in warps of their own take alternate
-            // stages of the running stage sequence (as the MMA issuers do), each both loads of
-            // its stages. The next slot's `empty` barrier is tested before this slot's loads are
-            // issued and the answer looked at after them. ----
+            // ---- TMA producer ----
             dependency_wait();
-            const int who = warp == 0 ? 0 : 1;
-            const int n_prod = ksteps >= 2 && g.n_stages >= 2 ? 2 : 1;
+            int stage = 0;
+            uint32_t phase = 0;
             uint32_t armed = 0;  // bit s: stage s holds a load nobody is known to have consumed
             uint32_t armed_parity = 0;
-            bool ok = who < n_prod && rounds > 0;
-            const bool active = ok;
+            bool ok = true;
             // a pair counts both CTAs' bytes on the leader's barrier
             const uint32_t full_local = smem_u32(&ctl->full[0]);
             const uint32_t full0 = PAIR && rank != 0 ? mapa(full_local, 0) : full_local;
-            const uint32_t empty0 = smem_u32(&ctl->empty[0]);
             const int b_rows = PAIR ? g.n_tile >> 1 : g.n_tile;  // filter rows this CTA loads
-            int stage = who;
-            uint32_t phase = 0;
-            long seq = who;   // position in the stage sequence; the first n_stages slots are free
-            uint32_t ready = 1;
-            int it = 0, ks = who;
-            int row0 = 0, brow0 = 0, row = 0, brow = 0, kw = 0, chunk = 0;
-            bool new_tile = true;
-            while (ok) {
-                if (new_tile) {
-                    // this thread's first stage of tile `it` is filter-tap step `ks` (0 or 1)
-                    int mt, nt;
-                    deal.at(g, it, mt, nt);
-                    row0 = g.lead + mt * BM - g.ph * g.wp - g.pw;  // tap (0,0)
-                    brow0 = nt * g.n_tile + (int)rank * b_rows;
-                    const int tap = ks / g.chunks_per_tap;
-                    chunk = ks - tap * g.chunks_per_tap;
-                    const int kh = tap / g.kw;
-                    kw = tap - kh * g.kw;
-                    row = row0 + kh * g.wp + kw;
-                    brow = brow0 + tap * g.ocp16;
-                    new_tile = false;
-                }
-                if (!ready) {
-                    const uint32_t ebar = empty0 + 8u * (uint32_t)stage;
+            for (int it = 0; ok && it < rounds; it++) {
+                int mt, nt;
+                deal.at(g, it, mt, nt);
+                int row = g.lead + mt * BM - g.ph * g.wp - g.pw;  // tap (0,0)
+                int brow = nt * g.n_tile + (int)rank * b_rows;
+                int kw = 0, chunk = 0;
+                for (int ks = 0; ks < ksteps; ks++) {
+                    const uint32_t ebar = smem_u32(&ctl->empty[stage]);
                     if (!mbar_try_wait(ebar, phase ^ 1)) {
                         ok = mbar_wait(ebar, phase ^ 1, abort_flag, g.error, 1, g.wait_ns);
                         if (!ok) break;
                     }
-                }
-                int next = stage + n_prod;
-                uint32_t next_phase = phase;
-                if (next >= g.n_stages) { next -= g.n_stages; next_phase ^= 1u; }
-                seq += n_prod;
-                ready = seq < g.n_stages ? 1u
-                                         : mbar_test(empty0 + 8u * (uint32_t)next, next_phase ^ 1u);
-                armed &= ~(1u << stage);
-                const uint32_t bar = full0 + 8u * (uint32_t)stage;
-                const uint32_t sa = stage0 + (uint32_t)stage * g.stage_bytes;
-                if (PAIR) {
-                    if (rank == 0) mbar_expect_tx(bar, 2u * g.tx_bytes);  // bar is local here
-                    tma_load_2d_pair(sa, &map_a, chunk * g.kchunk, row, bar);
-                    tma_load_2d_pair(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
-                } else {
-                    mbar_expect_tx(bar, g.tx_bytes);
-                    tma_load_2d(sa, &map_a, chunk * g.kchunk, row, bar);
-                    tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
-                }
-                armed |= 1u << stage;
-                armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-                stage = next;
-                phase = next_phase;
-                ks += n_prod;
-                if (ks >= ksteps) {
-                    do { ks -= ksteps; ++it; } while (ks >= ksteps);
-                    if (it >= rounds) break;
-                    new_tile = true;
-                } else {
-                    for (int adv = 0; adv < n_prod; adv++) {  // on by n_prod filter-tap steps
-                        if (++chunk == g.chunks_per_tap) {
-                            chunk = 0;
-                            brow += g.ocp16;
-                            if (++kw == g.kw) { kw = 0; row += g.wp - (g.kw - 1); }
-                            else row += 1;
-                        }
+                    armed &= ~(1u << stage);
+                    const uint32_t bar = full0 + 8u * (uint32_t)stage;
+                    const uint32_t sa = stage0 + (uint32_t)stage * g.stage_bytes;
+                    if (PAIR) {
+                        if (rank == 0) mbar_expect_tx(bar, 2u * g.tx_bytes);  // bar is local here
+                        tma_load_2d_pair(sa, &map_a, chunk * g.kchunk, row, bar);
+                        tma_load_2d_pair(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
+                    } else {
+                        mbar_expect_tx(bar, g.tx_bytes);
+                        tma_load_2d(sa, &map_a, chunk * g.kchunk, row, bar);
+                        tma_load_2d(sa + g.a_bytes, &map_b, chunk * g.kchunk, brow, bar);
+                    }
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == g.n_stages) { stage = 0; phase ^= 1; }
+                    if (++chunk == g.chunks_per_tap) {  // next filter tap
+                        chunk = 0;
+                        brow += g.ocp16;
+                        if (++kw == g.kw) { kw = 0; row += g.wp - (g.kw - 1); }
+                        else row += 1;
                     }
                 }
             }
-            if (active && !ok && rank == 0) {
+            if (!ok && rank == 0) {
                 // Something gave up. Loads already issued still land in this CTA's shared
                 // memory: wait for them (bounded) before the CTA may exit. (The partner of a
                 // pair cannot wait on the leader's barrier; it stays until the leader has got
