@@ -63,6 +63,10 @@ SHAPE_CASES = [
     # tiles; an NHWC result
     _c("pairs_151_tiles", 2140, 32, 40, 2, 2, 3, 3, ph=1, pw=1),
     _c("pairs_two_filter_tiles_of_192", 1060, 384, 8, 2, 2, 3, 3, ph=1, pw=1),
+    # the same with 128-byte channel chunks, where one position tile with a halo serves all taps of
+    # a filter row: two chunks with a tail of 72 channels, 3x3; one chunk, 5x5
+    _c("pairs_halo_ic200", 2140, 32, 200, 2, 2, 3, 3, ph=1, pw=1),
+    _c("pairs_halo_5x5", 1205, 32, 128, 2, 2, 5, 5, ph=2, pw=2),
 ]
 
 # Tensor formats other than NCHW/OIHW/NCHW

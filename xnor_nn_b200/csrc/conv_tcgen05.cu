@@ -86,6 +86,12 @@ struct TcArgs {
     int drop_commit;      // self-test: CTA 0 leaves out the commit that publishes its first tile
     int issuers;          // threads that issue MMAs: 1, or 2 taking alternate pipeline stages
     int n_stages;         // ring buffers in use
+    // Halo mode (pairs, 128-byte chunks, filters at least two taps wide): the position tile of a
+    // filter row is loaded once, with the kw - 1 positions that follow it, and serves all kw taps
+    // of the row (a tap is a row offset into the tile); the ring then holds filter tiles only.
+    int halo;             // 0, or rows of a halo tile (128 + 8)
+    int n_a_slots;        // halo tiles in flight
+    uint32_t a_slot_bytes, b_ring_off, b_slot_bytes, b_bytes;
     int kk_last;          // MMAs of a tap's last channel chunk: its 32-channel slices that hold
                           // channels at all (the chunk is padded with zero bytes to kchunk)
 };
@@ -100,6 +106,8 @@ struct __align__(16) Control {
     unsigned long long empty[kMaxStages];
     unsigned long long acc_full[2];
     unsigned long long acc_empty[2];
+    unsigned long long a_full[4];   // halo mode: a halo tile has landed / has been used up
+    unsigned long long a_empty[4];
     unsigned long long started[2];  // two issuers: the tile's first MMA (which overwrites) is out
     unsigned long long drain[2];
     uint32_t tmem_base;
@@ -496,6 +504,189 @@ __device__ __forceinline__ void mma_role(const TcArgs &g, Control *ctl, uint32_t
     }
 }
 
+// ---- halo mode: producer and MMA issuers -----------------------------------------------------------
+// Step order inside a tile: filter row kh, channel chunk, filter column kw (the sums are integers:
+// any order gives the same result). A group = the kw steps of one (kh, chunk): one halo tile of
+// g.halo positions in slot G % n_a_slots (G counts groups across tiles), kw filter tiles in
+// consecutive slots of the filter ring. A descriptor that starts r rows into a 128-byte-swizzled
+// tile reads rows r .. r + 127 of it (the swizzle is a function of the shared-memory address), so
+// tap kw of the group is the halo tile's descriptor advanced by kw rows.
+template <bool PAIR>
+__device__ __forceinline__ void producer_halo(const TcArgs &g, Control *ctl,
+                                              const CUtensorMap *map_a, const CUtensorMap *map_b,
+                                              uint32_t stage0, uint32_t rank) {
+    volatile int *abort_flag = &ctl->abort_flag;
+    const Deal<PAIR> deal(g);
+    const int rounds = deal.rounds(g);
+    const uint32_t full_l = smem_u32(&ctl->full[0]), afull_l = smem_u32(&ctl->a_full[0]);
+    // a pair counts both CTAs' bytes on the leader's barriers
+    const uint32_t full0 = PAIR && rank != 0 ? mapa(full_l, 0) : full_l;
+    const uint32_t afull0 = PAIR && rank != 0 ? mapa(afull_l, 0) : afull_l;
+    const uint32_t empty0 = smem_u32(&ctl->empty[0]), aempty0 = smem_u32(&ctl->a_empty[0]);
+    const int b_rows = PAIR ? g.n_tile >> 1 : g.n_tile;
+    const uint32_t mult = PAIR ? 2u : 1u;
+    const uint32_t a_bytes = (uint32_t)g.halo * (uint32_t)g.kchunk;
+    int sb = 0, sa = 0;
+    uint32_t pb = 0, pa = 0;
+    uint32_t armed_b = 0, parity_b = 0, armed_a = 0, parity_a = 0;
+    bool ok = true;
+    for (int it = 0; ok && it < rounds; it++) {
+        int mt, nt;
+        deal.at(g, it, mt, nt);
+        const int row0 = g.lead + mt * BM - g.ph * g.wp - g.pw;  // tap (0,0)
+        const int brow0 = nt * g.n_tile + (int)rank * b_rows;
+        for (int kh = 0; ok && kh < g.kh; kh++) {
+            for (int chunk = 0; ok && chunk < g.chunks_per_tap; chunk++) {
+                const uint32_t aebar = aempty0 + 8u * (uint32_t)sa;
+                if (!mbar_try_wait(aebar, pa ^ 1)) {
+                    ok = mbar_wait(aebar, pa ^ 1, abort_flag, g.error, 8, g.wait_ns);
+                    if (!ok) break;
+                }
+                const uint32_t abar = afull0 + 8u * (uint32_t)sa;
+                if (!PAIR || rank == 0) mbar_expect_tx(abar, mult * a_bytes);  // abar is local here
+                const uint32_t adst = stage0 + (uint32_t)sa * g.a_slot_bytes;
+                if (PAIR) tma_load_2d_pair(adst, map_a, chunk * g.kchunk, row0 + kh * g.wp, abar);
+                else tma_load_2d(adst, map_a, chunk * g.kchunk, row0 + kh * g.wp, abar);
+                armed_a |= 1u << sa;
+                parity_a = (parity_a & ~(1u << sa)) | (pa << sa);
+                if (++sa == g.n_a_slots) { sa = 0; pa ^= 1; }
+                int brow = brow0 + kh * g.kw * g.ocp16;
+                for (int kw = 0; kw < g.kw; kw++, brow += g.ocp16) {
+                    const uint32_t ebar = empty0 + 8u * (uint32_t)sb;
+                    if (!mbar_try_wait(ebar, pb ^ 1)) {
+                        ok = mbar_wait(ebar, pb ^ 1, abort_flag, g.error, 1, g.wait_ns);
+                        if (!ok) break;
+                    }
+                    const uint32_t bar = full0 + 8u * (uint32_t)sb;
+                    if (!PAIR || rank == 0) mbar_expect_tx(bar, mult * g.b_bytes);
+                    const uint32_t bdst = stage0 + g.b_ring_off + (uint32_t)sb * g.b_slot_bytes;
+                    if (PAIR) tma_load_2d_pair(bdst, map_b, chunk * g.kchunk, brow, bar);
+                    else tma_load_2d(bdst, map_b, chunk * g.kchunk, brow, bar);
+                    armed_b |= 1u << sb;
+                    parity_b = (parity_b & ~(1u << sb)) | (pb << sb);
+                    if (++sb == g.n_stages) { sb = 0; pb ^= 1; }
+                }
+            }
+        }
+    }
+    if (!ok && rank == 0) {
+        // Something gave up. Loads already issued still land in this CTA's shared memory: wait
+        // for them (bounded) before the CTA may exit.
+        for (int s = 0; s < g.n_stages; s++)
+            if (armed_b & (1u << s))
+                mbar_wait_quiet(full_l + 8u * (uint32_t)s, (parity_b >> s) & 1u, g.wait_ns);
+        for (int s = 0; s < g.n_a_slots; s++)
+            if (armed_a & (1u << s))
+                mbar_wait_quiet(afull_l + 8u * (uint32_t)s, (parity_a >> s) & 1u, g.wait_ns);
+    }
+}
+
+template <int KK, bool PAIR>
+__device__ __forceinline__ void mma_role_halo(const TcArgs &g, Control *ctl, uint32_t tmem_base,
+                                              uint32_t stage0, int who) {
+    volatile int *abort_flag = &ctl->abort_flag;
+    const int rounds = Deal<PAIR>(g).rounds(g);
+    if (rounds == 0) return;
+    const int ksteps = g.taps * g.chunks_per_tap;  // >= g.issuers; a multiple of g.kw
+    const int n_iss = g.issuers, kwn = g.kw;
+    const uint64_t hi = (uint64_t)g.desc_hi << 32;
+    const uint32_t a_lo0 = ((stage0 >> 4) & 0x3FFF) | (1u << 16);
+    const uint32_t b_lo0 = (((stage0 + g.b_ring_off) >> 4) & 0x3FFF) | (1u << 16);
+    const uint32_t a_units = g.a_slot_bytes >> 4, b_units = g.b_slot_bytes >> 4;
+    const uint32_t row_units = (uint32_t)g.kchunk >> 4;  // one position further
+    const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+    const uint32_t afull0 = smem_u32(&ctl->a_full[0]), aempty0 = smem_u32(&ctl->a_empty[0]);
+    int it = 0, ks = who;
+    int sb = who % g.n_stages;
+    uint32_t pb = 0;
+    // the group of this thread's current step: its column kw, its halo slot
+    int kw = who % kwn, sa = (who / kwn) % g.n_a_slots;
+    uint32_t pa = ((who / kwn) / g.n_a_slots) & 1u;
+    int chunk = (who / kwn) % g.chunks_per_tap;  // groups walk the chunks, then the filter rows
+    bool ok = true, entered = false, a_seen = false;
+    for (;;) {
+        const int b = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!entered) {
+            if (ks == 0)
+                ok = mbar_wait(smem_u32(&ctl->acc_empty[b]), acc_phase ^ 1, abort_flag, g.error, 2,
+                               g.wait_ns);
+            else if (n_iss > 1)
+                ok = mbar_wait(smem_u32(&ctl->started[b]), acc_phase, abort_flag, g.error, 6,
+                               g.wait_ns);
+            if (!ok) break;
+            fence_after();
+            entered = true;
+        }
+        if (!a_seen) {  // first step of this thread in the group: the halo tile must have landed
+            const uint32_t abar = afull0 + 8u * (uint32_t)sa;
+            if (!mbar_try_wait(abar, pa)) {
+                ok = mbar_wait(abar, pa, abort_flag, g.error, 9, g.wait_ns);
+                if (!ok) break;
+            }
+            a_seen = true;
+        }
+        const uint32_t fbar = full0 + 8u * (uint32_t)sb;
+        if (!mbar_try_wait(fbar, pb)) {
+            ok = mbar_wait(fbar, pb, abort_flag, g.error, 3, g.wait_ns);
+            if (!ok) break;
+        }
+        fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * g.n_tile);
+        const uint64_t adesc =
+            hi | (uint64_t)(a_lo0 + (uint32_t)sa * a_units + (uint32_t)kw * row_units);
+        const uint64_t bdesc = hi | (uint64_t)(b_lo0 + (uint32_t)sb * b_units);
+        const int kk = chunk == g.chunks_per_tap - 1 ? g.kk_last : KK;
+#pragma unroll
+        for (int k = 0; k < KK; k++) {
+            if (k < kk) {
+                if (PAIR)
+                    mma_i8_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
+                                g.idesc, (k == 0 && ks == 0) ? 0u : 1u);
+                else
+                    mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), g.idesc,
+                           (k == 0 && ks == 0) ? 0u : 1u);
+            }
+        }
+        if (PAIR) commit_pair(empty0 + 8u * (uint32_t)sb);
+        else commit(empty0 + 8u * (uint32_t)sb);
+        if (n_iss > 1 && ks == 0) {
+            fence_before();
+            mbar_arrive(smem_u32(&ctl->started[b]));
+        }
+        sb += n_iss;
+        if (sb >= g.n_stages) { sb -= g.n_stages; pb ^= 1u; }
+        kw += n_iss;
+        if (kw >= kwn) {
+            // this thread's last step of the group is issued: its reads of the halo tile are
+            // covered by this commit (both issuers commit: the barrier counts them)
+            if (PAIR) commit_pair(aempty0 + 8u * (uint32_t)sa);
+            else commit(aempty0 + 8u * (uint32_t)sa);
+            do {
+                kw -= kwn;
+                if (++sa == g.n_a_slots) { sa = 0; pa ^= 1u; }
+                if (++chunk == g.chunks_per_tap) chunk = 0;
+            } while (kw >= kwn);
+            a_seen = false;
+        }
+        ks += n_iss;
+        if (ks >= ksteps) {  // this thread's share of the tile is issued
+            ks -= ksteps;
+            if (!(g.drop_commit && it == 0 && blockIdx.x == 0)) {
+                if (PAIR) commit_pair(smem_u32(&ctl->acc_full[b]));
+                else commit(smem_u32(&ctl->acc_full[b]));
+            }
+            entered = false;
+            if (++it >= rounds) break;
+        }
+    }
+    if (!ok) {
+        if (PAIR) commit_pair(smem_u32(&ctl->drain[who]));
+        else commit(smem_u32(&ctl->drain[who]));
+        mbar_wait_quiet(smem_u32(&ctl->drain[who]), 0, g.wait_ns);
+    }
+}
+
 // KK = tcgen05.mma instructions per pipeline stage (kchunk / 32).
 // PAIR: the grid is made of clusters of two CTAs that share tiles of 256 positions x N filters
 // (tcgen05 cta_group::2). Each CTA loads its own 128 positions and its half of the filter tile,
@@ -521,6 +712,10 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int s = 0; s < g.n_stages; s++) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
             mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int a = 0; a < 4; a++) {
+            mbar_init(smem_u32(&ctl->a_full[a]), 1);
+            mbar_init(smem_u32(&ctl->a_empty[a]), (uint32_t)g.issuers);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(smem_u32(&ctl->acc_full[b]), (uint32_t)g.issuers);
@@ -567,6 +762,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) {
             // ---- TMA producer ----
             dependency_wait();
+            if (g.halo) {
+                producer_halo<PAIR>(g, ctl, &map_a, &map_b, stage0, rank);
+            } else {
             int stage = 0;
             uint32_t phase = 0;
             uint32_t armed = 0;  // bit s: stage s holds a load nobody is known to have consumed
@@ -622,11 +820,14 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                         g.wait_ns);
                     }
             }
+            }
         }
     } else if (warp == 1 || warp == kIssuer2Warp) {
         const int who = warp == 1 ? 0 : 1;
-        if (lane == 0 && who < g.issuers && rank == 0)
-            mma_role<KK, PAIR>(g, ctl, tmem_base, stage0, who);
+        if (lane == 0 && who < g.issuers && rank == 0) {
+            if (g.halo) mma_role_halo<KK, PAIR>(g, ctl, tmem_base, stage0, who);
+            else mma_role<KK, PAIR>(g, ctl, tmem_base, stage0, who);
+        }
         __syncwarp();
     } else {
         // ---- epilogue warps: stage alpha among themselves, then drain accumulators ----
@@ -680,12 +881,6 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     const bool pair = !next && p.n_tile % 32 == 0 && m_tiles >= 2 &&
                       (long)m_tiles * (p.ocp16 / p.n_tile) > sms;
     const int b_rows = pair ? p.n_tile / 2 : p.n_tile;  // filter rows a CTA loads per stage
-    CUtensorMap map_a, map_b;
-    if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk, BM) ||
-        !encode_bytes_2d(&map_b, bin_w, (uint64_t)p.kh * p.kw * p.ocp16, (uint64_t)p.icp,
-                         (uint32_t)p.kchunk, (uint32_t)b_rows))
-        return cudaErrorNotSupported;
-
     TcArgs g;
     g.alpha = alpha; g.kmap = k; g.amap = a; g.kmap_out = k_out; g.dst = dst; g.sums = sums;
     g.error = error_word;
@@ -724,9 +919,31 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
     g.kk_last = (p.ic - (g.chunks_per_tap - 1) * p.kchunk + 31) / 32;
     // as many ring buffers as fit beside the control block
     const size_t room = 227 * 1024 - 1024 - kControlBytes;
-    g.n_stages = (int)(room / g.stage_bytes);
-    if (g.n_stages > kMaxStages) g.n_stages = kMaxStages;
+    g.halo = 0; g.n_a_slots = 0; g.a_slot_bytes = 0; g.b_ring_off = 0; g.b_slot_bytes = 0;
+    g.b_bytes = (uint32_t)(b_rows * p.kchunk);
+    bool halo = pair && p.kchunk == 128 && p.kw >= 2 && p.kw <= 9 && g.issuers <= p.kw;
+    if (halo) {
+        // three halo tiles of 136 positions, the rest of the room for filter tiles
+        g.halo = BM + 8;
+        g.n_a_slots = 3;
+        g.a_slot_bytes = (uint32_t)(g.halo * p.kchunk + 1023) & ~1023u;
+        g.b_slot_bytes = (g.b_bytes + 1023u) & ~1023u;
+        g.b_ring_off = (uint32_t)g.n_a_slots * g.a_slot_bytes;
+        g.n_stages = (int)((room - g.b_ring_off) / g.b_slot_bytes);
+        if (g.n_stages > kMaxStages) g.n_stages = kMaxStages;
+        if (g.n_stages < 4) { g.halo = 0; halo = false; }
+    }
+    if (!halo) {
+        g.n_stages = (int)(room / g.stage_bytes);
+        if (g.n_stages > kMaxStages) g.n_stages = kMaxStages;
+    }
     if (g.n_stages < 2) return cudaErrorNotSupported;
+    CUtensorMap map_a, map_b;
+    if (!encode_bytes_2d(&map_a, bin_src, (uint64_t)p.rows, (uint64_t)p.icp, (uint32_t)p.kchunk,
+                         (uint32_t)(halo ? g.halo : BM)) ||
+        !encode_bytes_2d(&map_b, bin_w, (uint64_t)p.kh * p.kw * p.ocp16, (uint64_t)p.icp,
+                         (uint32_t)p.kchunk, (uint32_t)b_rows))
+        return cudaErrorNotSupported;
 
     const int kk = p.kchunk / 32;
     void (*kernel)(CUtensorMap, CUtensorMap, TcArgs) =
@@ -736,7 +953,9 @@ cudaError_t launch_conv_tcgen05(const Plan &p, const void *bin_src, const void *
              : (kk == 4   ? conv_tcgen05_kernel<4, false>
                 : kk == 2 ? conv_tcgen05_kernel<2, false>
                           : conv_tcgen05_kernel<1, false>);
-    size_t smem = 1024 + kControlBytes + (size_t)g.n_stages * g.stage_bytes;
+    size_t smem = 1024 + kControlBytes +
+                  (halo ? (size_t)g.b_ring_off + (size_t)g.n_stages * g.b_slot_bytes
+                        : (size_t)g.n_stages * g.stage_bytes);
     // At least 120 KB of shared memory so that one CTA owns the SM and all 512 TMEM columns.
     if (smem < 120 * 1024) smem = 120 * 1024;
     // per device and kernel, once: the opt-in to large dynamic shared memory, the SM count and
