@@ -145,6 +145,13 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append((time.time(), line.strip()))
 
+    def wait_live(self, seconds=5.0):
+        """Blocks until the first sample has arrived (nvidia-smi needs a few hundred ms to start,
+        more than the timed regions last), or `seconds` have passed."""
+        t_end = time.time() + seconds
+        while self.proc and not self.rows and time.time() < t_end and self.proc.poll() is None:
+            time.sleep(0.005)
+
     def stop(self):
         if self.proc:
             self.proc.terminate()
@@ -456,6 +463,8 @@ def measure_layer(xb, torch, args, cfg_name, kernel, rank, world, dist, probe, b
             graphs[i % lay.sets].replay()
 
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 and not brief else None
+    if sampler:
+        sampler.wait_live()
     for i in range(max(3, args.warmup)):
         step(i)
     barrier()
