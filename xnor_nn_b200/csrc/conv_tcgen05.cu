@@ -213,9 +213,17 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
             // Given up: touch nothing any more. The chained epilogue's warps of a quadrant meet
             // on a named barrier once per tile; a warp that has given up keeps that appointment
             // so that one that has not (yet) cannot be left waiting there.
-            if (!g.emit_bin) break;
-            bar_sync(1 + quad, 32 * (kEpiWarps / 4));
-            continue;
+            if (g.emit_bin) {
+                bar_sync(1 + quad, 32 * (kEpiWarps / 4));
+                continue;
+            }
+            // The NCHW float epilogue's column groups meet three times per tile (all tiles of a
+            // CTA but its last): the same appointments are kept here.
+            if (!g.sums && !g.dst_nhwc && it + 1 < rounds && g.n_tile == 256) {
+                for (int w = 0; w < kEpiWarps / 4 - 1; w++) bar_sync(10, 32 * kEpiWarps);
+                continue;
+            }
+            break;
         }
         fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * g.n_tile);
@@ -306,6 +314,15 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
             // store instruction writes one contiguous run.
             float *out = g.dst + ((long)n * g.oc + oc0) * ohw + r;
             const float *al = alpha_in_smem ? ctl->alpha + oc0 : g.alpha + oc0;
+            // Except for a CTA's last tile the four column groups store one after the other
+            // (three meetings of all epilogue warps per tile, column group c stores between the
+            // c-th and the next): the stores of a tile then leave the SM over about twice the
+            // time, which leaves the SM's request port more room for the next tile's operand
+            // loads (conv4 32.7 -> 31.6 us, VGG 78.6 -> 76.9). Only for tiles of 256 filters: with
+            // narrower ones (conv3, N = 192) a tile's MMAs are over sooner than its epilogue
+            // spread out like this, and the whole step got slower (55.1 -> 57.7 us).
+            const bool paced = it + 1 < rounds && g.n_tile == 256;
+            if (paced) for (int w = 0; w < cgroup; w++) bar_sync(10, 32 * kEpiWarps);
             for (int c0 = 32 * cgroup; c0 < g.n_tile; c0 += 32 * cgroups) {
                 uint32_t v[32];
                 if (c0 + 32 <= g.n_tile) {
@@ -338,6 +355,7 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
                     }
                 }
             }
+            if (paced) for (int w = cgroup; w < kEpiWarps / 4 - 1; w++) bar_sync(10, 32 * kEpiWarps);
         } else if (!g.sums && g.dst_nhwc && (g.oc & 3) == 0) {
             // NHWC floats: a thread owns one pixel and 16 neighbouring filters at a time, which
             // are contiguous in the result: four 16-byte stores.
