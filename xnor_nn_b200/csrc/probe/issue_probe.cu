@@ -11,6 +11,9 @@
 //                      tile + one 4-D box of 169 rows, ring of four buffers), one SM and all SMs
 //   store_cycles       cycles per global store instruction of one warp, by access pattern
 //   bulk_store         a 21.6 KB shared->global bulk store alone and beside the TMA producer
+//   umma_row_offset    whether a UMMA descriptor that starts r rows (r x 128 B, r = 0..7) into a
+//                      128-byte-swizzled tile reads rows r .. r+127 of it (what lets one position
+//                      tile with a halo serve all taps of a filter row): wrong results per r
 //
 // Every wait in here is bounded (2 s), no kernel waits on another.
 #include <cuda.h>
@@ -162,6 +165,57 @@ stores(uint8_t *out, int pattern, int warps, int iters, long long *res) {
     if (blockIdx.x == 0 && threadIdx.x == 0) res[0] = clock64() - t0;
 }
 
+// ---- a descriptor that starts r rows into a swizzled tile ---------------------------------------
+// A[m][k] known bytes (136 rows), B[n][k] = 1 at k == n and 2 at k == n + 32 (32 rows), K = 64:
+// D[m][n] = A[m + r][n] + 2 A[m + r][n + 32] if the descriptor reads rows r .. r + 127.
+__global__ void __launch_bounds__(128, 1)
+row_offset(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+           int r, int32_t *out, int *err) {
+    extern __shared__ uint8_t raw[];
+    uint8_t *base = (uint8_t *)(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
+    __shared__ unsigned long long full, done;
+    __shared__ uint32_t tm_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&full), 1);
+        mbar_init(smem_u32(&done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(smem_u32(&tm_s), 32);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tm = tm_s;
+    const uint32_t sa = smem_u32(base), sb = sa + 136 * 128;
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(smem_u32(&full), 136 * 128 + 32 * 128);
+        tma_load_2d(sa, &map_a, 0, 0, smem_u32(&full));
+        tma_load_2d(sb, &map_b, 0, 0, smem_u32(&full));
+        if (!wait_bounded(smem_u32(&full), 0)) *err = 3;
+        fence_after();
+        const uint64_t hi = (uint64_t)(64u | (1u << 14) | (2u << 29)) << 32;
+        const uint64_t ad = hi | (uint64_t)((((sa + r * 128) >> 4) & 0x3FFF) | (1u << 16));
+        const uint64_t bd = hi | (uint64_t)(((sb >> 4) & 0x3FFF) | (1u << 16));
+        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(32 >> 3) << 17) | (8u << 24);
+        mma_i8(tm, ad, bd, idesc, 0u);
+        mma_i8(tm, ad + 2, bd + 2, idesc, 1u);
+        commit(smem_u32(&done));
+        if (!wait_bounded(smem_u32(&done), 0)) *err = 4;
+    }
+    __syncthreads();
+    fence_after();
+    uint32_t v[32];
+    ld32(tm + ((uint32_t)(warp * 32) << 16), v);
+    wait_ld();
+    for (int j = 0; j < 32; j++) out[(warp * 32 + lane) * 32 + j] = (int)v[j];
+    fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        fence_after();
+        tmem_free(tm, 32);
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -267,6 +321,46 @@ int main() {
             first = false;
         }
     printf("}, ");
+
+    // descriptor row offsets
+    {
+        static int8_t ha[160 * 128], hb[32 * 128];
+        for (int m = 0; m < 160; m++)
+            for (int k = 0; k < 128; k++) ha[m * 128 + k] = (int8_t)((m * 7 + k * 3) % 11 - 5);
+        memset(hb, 0, sizeof hb);
+        for (int n = 0; n < 32; n++) { hb[n * 128 + n] = 1; hb[n * 128 + n + 32] = 2; }
+        int8_t *da, *db;
+        int32_t *dout;
+        cudaMalloc(&da, sizeof ha);
+        cudaMalloc(&db, sizeof hb);
+        cudaMalloc(&dout, 128 * 32 * 4);
+        cudaMemcpy(da, ha, sizeof ha, cudaMemcpyHostToDevice);
+        cudaMemcpy(db, hb, sizeof hb, cudaMemcpyHostToDevice);
+        CUtensorMap ma, mb2;
+        const cuuint64_t da2[2] = {128, 160}, db2[2] = {128, 32}, st[1] = {128};
+        const cuuint32_t ba[2] = {128, 136}, bb[2] = {128, 32};
+        printf("\"umma_row_offset_wrong_results\": {");
+        if (enc(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, da, da2, st, ba, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS &&
+            enc(&mb2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, db, db2, st, bb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+            cudaFuncSetAttribute(row_offset, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+            static int32_t ho[128 * 32];
+            for (int r = 0; r < 8; r++) {
+                row_offset<<<1, 128, 64 * 1024>>>(ma, mb2, r, dout, err);
+                cudaDeviceSynchronize();
+                cudaMemcpy(ho, dout, sizeof ho, cudaMemcpyDeviceToHost);
+                int bad = 0;
+                for (int m = 0; m < 128; m++)
+                    for (int n = 0; n < 32; n++)
+                        bad += ho[m * 32 + n] != ha[(m + r) * 128 + n] + 2 * ha[(m + r) * 128 + n + 32];
+                printf("%s\"r=%d\": %d", r ? ", " : "", r, bad);
+            }
+        }
+        printf("}, ");
+    }
 
     int flagged = 0;
     cudaMemcpy(&flagged, err, 4, cudaMemcpyDeviceToHost);
