@@ -27,7 +27,11 @@
 // Layers of more than one round of tiles run as clusters of two CTAs on tcgen05 cta_group::2:
 // the pair shares a tile of 256 positions x N filters, each CTA loads its own 128 positions and
 // half of the filter tile, the leader issues M = 256 instructions for both, and each CTA's
-// epilogue drains its own tensor memory.
+// epilogue drains its own tensor memory. With 128-byte channel chunks a pair loads a position
+// tile only once per filter row and chunk, with a halo of the positions that follow it, and the
+// taps of the row read that tile at row offsets (producer_halo / mma_role_halo): what bounds the
+// kernel is the number of requests an SM can send towards L2, operand reads and result stores
+// together.
 //
 // The epilogue has three forms: floats in NCHW (a warp store is one contiguous run of a filter
 // plane), floats in NHWC (a thread owns whole 32-byte sectors and writes them with 256-bit
