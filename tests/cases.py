@@ -67,6 +67,9 @@ SHAPE_CASES = [
     # a filter row: two chunks with a tail of 72 channels, 3x3; one chunk, 5x5
     _c("pairs_halo_ic200", 2140, 32, 200, 2, 2, 3, 3, ph=1, pw=1),
     _c("pairs_halo_5x5", 1205, 32, 128, 2, 2, 5, 5, ph=2, pw=2),
+    # a filter tile that does not split into two UMMA-sized halves (48 filters): as many tiles, but
+    # on single CTAs, each with two tiles or one
+    _c("many_tiles_single_ctas", 2140, 48, 40, 2, 2, 3, 3, ph=1, pw=1),
 ]
 
 # Tensor formats other than NCHW/OIHW/NCHW
