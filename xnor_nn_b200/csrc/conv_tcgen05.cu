@@ -344,18 +344,21 @@ __device__ __forceinline__ void epilogue_role(const TcArgs &g, Control *ctl, uin
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
                             const float4 a = a4[j >> 2];
-                            o[0] = __fmul_rn(__fmul_rn((float)(int)v[j], a.x), kk);
-                            o[ohw] = __fmul_rn(__fmul_rn((float)(int)v[j + 1], a.y), kk);
-                            o[2 * ohw] = __fmul_rn(__fmul_rn((float)(int)v[j + 2], a.z), kk);
-                            o[3 * ohw] = __fmul_rn(__fmul_rn((float)(int)v[j + 3], a.w), kk);
+                            // streaming stores: the result is not read again by this library,
+                            // and lines that leave L2 while this kernel runs (which needs little
+                            // of HBM) do not have to leave it under the next, bandwidth-bound pass
+                            __stcs(o, __fmul_rn(__fmul_rn((float)(int)v[j], a.x), kk));
+                            __stcs(o + ohw, __fmul_rn(__fmul_rn((float)(int)v[j + 1], a.y), kk));
+                            __stcs(o + 2 * ohw, __fmul_rn(__fmul_rn((float)(int)v[j + 2], a.z), kk));
+                            __stcs(o + 3 * ohw, __fmul_rn(__fmul_rn((float)(int)v[j + 3], a.w), kk));
                             o += 4 * ohw;
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; j++)
                             if (j < lim)
-                                o[(long)j * ohw] =
-                                    __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk);
+                                __stcs(o + (long)j * ohw,
+                                       __fmul_rn(__fmul_rn((float)(int)v[j], al[c0 + j]), kk));
                     }
                 }
             }
