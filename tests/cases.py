@@ -70,6 +70,10 @@ SHAPE_CASES = [
     # a filter tile that does not split into two UMMA-sized halves (48 filters): as many tiles, but
     # on single CTAs, each with two tiles or one
     _c("many_tiles_single_ctas", 2140, 48, 40, 2, 2, 3, 3, ph=1, pw=1),
+    # many blocks of the activation packer on sources of one channel chunk (96 channels: chunks of
+    # 96; 100: a chunk of 128 with a channel tail)
+    _c("packer_many_blocks_ic96", 250, 16, 96, 13, 13, 3, 3, ph=1, pw=1),
+    _c("packer_many_blocks_ic100", 250, 16, 100, 13, 13, 3, 3, ph=1, pw=1),
 ]
 
 # Tensor formats other than NCHW/OIHW/NCHW

@@ -122,26 +122,50 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 // A block of four warps owns 32 neighbouring pixels and walks the channels in chunks of 128.
 // All warps load (lane = pixel, warp w the w-th quarter of the chunk's channels, so a load
 // instruction reads one 128-byte line of a channel plane; 32 independent loads per thread, issued
-// one chunk ahead so that they are in flight while the previous chunk is consumed). |x|/IC goes to a float tile and the sign byte to a byte
-// tile in shared memory. Warp 0 then adds the float tile up channel by channel, one lane per
-// pixel, which keeps upstream's summation order, while the other warps copy the byte tile out
-// as one coalesced 128-byte line per pixel. Seven blocks are resident per SM (72 registers per
-// thread, and the shared-memory carve-out is sized to match).
+// one chunk ahead so that they are in flight while the previous chunk is consumed). |x|/IC goes
+// to a float tile and the sign byte to a byte tile in shared memory, both pixel-major. Warp 0 then
+// adds the float tile up channel by channel, one lane per pixel, which keeps upstream's summation
+// order, while the other warps copy the byte tile out, 8 bytes per lane, a pixel's 128-byte line
+// per half warp. Seven blocks are resident per SM (72 registers per thread, and the shared-memory
+// carve-out is sized to match).
+//
+// The kernel is as much bound by instruction issue as by memory (a profile of the first version
+// on the 96-channel AlexNet layer: 29 instructions issued per global load, the schedulers busy
+// in 69 % of the active cycles, DRAM at 31 %). Hence: the sign bytes of four floats come from
+// three byte permutes and one logic operation; both tiles are written and read with 8- and
+// 16-byte shared-memory accesses, their rows padded so that these stay free of bank conflicts;
+// pixel coordinates are 32-bit (the host sends anything larger to the generic kernel).
 //
 // TPER = channels per warp and chunk = loads per thread and chunk: 32 (chunks of 128 channels)
 // or 24 (chunks of 96), the latter for channel counts that are a multiple of 96 but not of 128
 // (AlexNet conv2), where a 128-channel chunk would leave a quarter of the threads without work.
-// Bytes past the last channel of a packed row are never written: they are zero from allocation.
+// Bytes past the last channel of a packed row are zero from allocation, and only zeros are
+// ever written there.
 constexpr int TPX = 32;    // pixels per block
 constexpr int TWARPS = 4;
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// The +-1 bytes of four floats, the first in the lowest byte: sign bit set -> 0xFF, clear -> 0x01.
+// A selector nibble of 0xB / 0xF replicates the top bit of byte 3 of the first / second operand.
+__device__ __forceinline__ uint32_t sign_bytes(float a, float b, float c, float d) {
+    const uint32_t ab = prmt(__float_as_uint(a), __float_as_uint(b), 0xFBFBu);
+    const uint32_t cd = prmt(__float_as_uint(c), __float_as_uint(d), 0xFBFBu);
+    return (prmt(ab, cd, 0x5410u) & 0xFEFEFEFEu) ^ 0x01010101u;
+}
 
 template <bool WITH_A, bool WITH_PACK, int TPER>
 __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const BinArgs g) {
     constexpr int TCC = TPER * TWARPS;  // channels per chunk
-    constexpr int TLD = TCC + 4;
-    __shared__ float f_s[WITH_A ? TCC * TPX : 1];
-    __shared__ __align__(16) uint8_t b_s[WITH_PACK ? TPX * TLD : 4];
-    __shared__ long row_s[TPX];
+    constexpr int FLD = TCC + 4;        // floats per pixel of the float tile
+    constexpr int TLD = TCC + 8;        // bytes per pixel of the byte tile
+    __shared__ __align__(16) float f_s[WITH_A ? TPX * FLD : 4];
+    __shared__ __align__(16) uint8_t b_s[WITH_PACK ? TPX * TLD : 8];
+    __shared__ long row_s[TPX];  // a pixel's packed row, as an offset in units of 8 bytes
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // The dependent grid (the convolution) may be launched once every block of this grid has
@@ -150,20 +174,22 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
     // triggering at the end of the block). They wait for this grid's results themselves.
     dependency_release();
     dependency_wait();  // nothing of an earlier kernel is read or overwritten before this
-    const long px = (long)blockIdx.x * TPX + lane;
-    const bool live = px < g.n_px;
-    const int n = live ? (int)(px / g.hw) : 0;
-    const int r = live ? (int)(px - (long)n * g.hw) : 0;
-    const float *p = g.src + n * g.img_stride + r;
-    if (warp == 0) row_s[lane] = live ? packed_row<kBytesFramed>(g, px) : -1;
+    const unsigned px = blockIdx.x * TPX + lane;
+    const bool live = px < (unsigned)g.n_px;
+    const unsigned n = live ? px / (unsigned)g.hw : 0u;
+    const unsigned r = live ? px - n * (unsigned)g.hw : 0u;
+    if (warp == 0) {
+        const unsigned h = r / (unsigned)g.iw, w = r - h * (unsigned)g.iw;
+        const long row = g.lead + ((long)n * g.hp + h) * g.wp + w;
+        row_s[lane] = live ? row * (g.words >> 1) : -1;
+    }
 
     // channel extent walked: the channels, rounded up to whole 32-bit words of the packed row
     const int c_end = WITH_PACK ? min(g.words * 4, (g.ic + 3) & ~3) : g.ic;
     float acc = 0.f;
-    // Warp w owns the 32 consecutive channels [32w, 32w+32) of every chunk, so four of its sign
-    // bytes make one 32-bit word of the packed row.
-    const float *pw = p + (long)(TPER * warp) * g.hw;
+    // Warp w owns the TPER consecutive channels [TPER w, TPER (w + 1)) of every chunk.
     const int cw = TPER * warp;  // first channel of this warp inside a chunk
+    const float *pw = g.src + (long)n * g.img_stride + r + (long)cw * g.hw;
     float v[TPER];
     if (live && TCC <= g.ic) {
 #pragma unroll
@@ -176,25 +202,30 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
     for (int c0 = 0; c0 < c_end; c0 += TCC) {
         const bool full = c0 + TCC <= g.ic;  // no channel tail in this chunk
         if (WITH_A) {
+            float4 *frow = reinterpret_cast<float4 *>(f_s + lane * FLD + cw);
 #pragma unroll
-            for (int i = 0; i < TPER; i++)
-                f_s[(cw + i) * TPX + lane] = __fmul_rn(fabsf(v[i]), g.inv_ic);
+            for (int j = 0; j < TPER / 4; j++)
+                frow[j] = make_float4(__fmul_rn(fabsf(v[4 * j]), g.inv_ic),
+                                      __fmul_rn(fabsf(v[4 * j + 1]), g.inv_ic),
+                                      __fmul_rn(fabsf(v[4 * j + 2]), g.inv_ic),
+                                      __fmul_rn(fabsf(v[4 * j + 3]), g.inv_ic));
         }
         if (WITH_PACK) {
-            uint32_t *brow = reinterpret_cast<uint32_t *>(b_s + lane * TLD) + cw / 4;
+            uint2 *brow = reinterpret_cast<uint2 *>(b_s + lane * TLD + cw);
 #pragma unroll
-            for (int j = 0; j < TPER / 4; j++) {
-                // sign bit set -> 0xFF (-1), clear -> 0x01 (+1): 0x01 ^ (sign * 0xFE) per byte
-                const uint32_t m = (__float_as_uint(v[4 * j]) >> 31) |
-                                   ((__float_as_uint(v[4 * j + 1]) >> 31) << 8) |
-                                   ((__float_as_uint(v[4 * j + 2]) >> 31) << 16) |
-                                   ((__float_as_uint(v[4 * j + 3]) >> 31) << 24);
-                uint32_t word = 0x01010101u ^ (m * 0xFEu);
-                if (!full) {  // channels past the last one are zero bytes
-                    const int left = g.ic - (c0 + cw + 4 * j);
-                    word = left >= 4 ? word : left <= 0 ? 0u : (word & (0xFFFFFFFFu >> (8 * (4 - left))));
+            for (int j = 0; j < TPER / 8; j++) {
+                uint32_t w2[2];
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    const int c = 8 * j + 4 * q;
+                    uint32_t word = sign_bytes(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                    if (!full) {  // channels past the last one are zero bytes
+                        const int left = g.ic - (c0 + cw + c);
+                        word = left >= 4 ? word : left <= 0 ? 0u : (word & (0xFFFFFFFFu >> (8 * (4 - left))));
+                    }
+                    w2[q] = word;
                 }
-                brow[j] = word;
+                brow[j] = make_uint2(w2[0], w2[1]);
             }
         }
         __syncthreads();
@@ -211,39 +242,43 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
         }
         if (WITH_A && warp == 0) {
             const int nc = min(TCC, g.ic - c0);
+            const float *fr = f_s + lane * FLD;
             if (nc == TCC) {
 #pragma unroll
                 for (int j0 = 0; j0 < TCC; j0 += 16) {
-                    float t[16];
+                    float4 t[4];
 #pragma unroll
-                    for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
+                    for (int j = 0; j < 4; j++) t[j] = *reinterpret_cast<const float4 *>(fr + j0 + 4 * j);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
+                    for (int j = 0; j < 4; j++) {
+                        acc = __fadd_rn(acc, t[j].x);
+                        acc = __fadd_rn(acc, t[j].y);
+                        acc = __fadd_rn(acc, t[j].z);
+                        acc = __fadd_rn(acc, t[j].w);
+                    }
                 }
-            } else {
-                // channel tail: same order, groups of 16 loads in flight while they fit
-                int j0 = 0;
-                for (; j0 + 16 <= nc; j0 += 16) {
-                    float t[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) t[j] = f_s[(j0 + j) * TPX + lane];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, t[j]);
+            } else {  // channel tail: same order
+                int j = 0;
+                for (; j + 4 <= nc; j += 4) {
+                    const float4 t = *reinterpret_cast<const float4 *>(fr + j);
+                    acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, t.x), t.y), t.z), t.w);
                 }
-                for (; j0 < nc; j0++) acc = __fadd_rn(acc, f_s[j0 * TPX + lane]);
+                for (; j < nc; j++) acc = __fadd_rn(acc, fr[j]);
             }
         } else if (WITH_PACK) {
-            // a warp writes one pixel per pass: 32 lanes x 4 bytes, one 128-byte line
+            // half a warp writes one pixel per pass: 16 (12) lanes x 8 bytes, one 128-byte line
             const int first = WITH_A ? warp - 1 : warp, step = WITH_A ? TWARPS - 1 : TWARPS;
-            const int nwords = (min(TCC, c_end - c0) + 3) / 4;
-            constexpr int WPP = TCC / 4;   // 32-bit words per pixel and chunk
-            constexpr int PPW = 32 / WPP;  // pixels a warp writes per pass
-            const int half = lane / WPP, wl = lane % WPP;
-            for (int pi = PPW * first + half; pi < TPX; pi += PPW * step) {
-                const long row = row_s[pi];
-                if (row >= 0 && wl < nwords && half < PPW)
-                    ((uint32_t *)g.out)[row * g.words + c0 / 4 + wl] =
-                        *reinterpret_cast<const uint32_t *>(&b_s[pi * TLD + 4 * wl]);
+            const int n8 = (min(TCC, c_end - c0) + 7) / 8;
+            constexpr int LPP = TCC / 8;   // lanes per pixel and chunk
+            constexpr int PPW = 32 / LPP;  // pixels a warp writes per pass
+            const int sub = lane / LPP, wl = lane % LPP;
+            if (sub < PPW && wl < n8) {
+                for (int pi = PPW * first + sub; pi < TPX; pi += PPW * step) {
+                    const long row = row_s[pi];
+                    if (row >= 0)
+                        reinterpret_cast<uint2 *>(g.out)[row + (c0 >> 3) + wl] =
+                            *reinterpret_cast<const uint2 *>(&b_s[pi * TLD + 8 * wl]);
+                }
             }
         }
         __syncthreads();
@@ -301,7 +336,7 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
     const int threads = 128;
     const unsigned blocks = (unsigned)((g.n_px + threads - 1) / threads);
     if (blocks == 0) return cudaSuccess;
-    if (!p.src_nhwc && (p.family == kTcgen05 || !WITH_PACK)) {
+    if (!p.src_nhwc && (p.family == kTcgen05 || !WITH_PACK) && g.n_px < (1L << 31) - TPX) {
         // Shared-memory carve-out sized for kResidentBlocks blocks per SM, once per device. Left
         // to itself the driver sizes it for as many blocks as the thread count allows, which
         // leaves the L1 too small for the loads in flight; a kernel that streams with 32 loads
