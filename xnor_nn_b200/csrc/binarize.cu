@@ -158,6 +158,13 @@ __device__ __forceinline__ uint32_t sign_bytes(float a, float b, float c, float 
     return (prmt(ab, cd, 0x5410u) & 0xFEFEFEFEu) ^ 0x01010101u;
 }
 
+// Element i of a column of floats whose rows are `pitch` bytes apart: one 32 x 32 + 64-bit
+// multiply-add per address (the index arithmetic on 64-bit element offsets that the plain
+// expression compiles to took seven integer instructions per load).
+__device__ __forceinline__ const float *row_ptr(const float *p, unsigned i, unsigned pitch) {
+    return reinterpret_cast<const float *>(reinterpret_cast<const char *>(p) + (size_t)(i * pitch));
+}
+
 template <bool WITH_A, bool WITH_PACK, int TPER>
 __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const BinArgs g) {
     constexpr int TCC = TPER * TWARPS;  // channels per chunk
@@ -176,6 +183,7 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
     dependency_wait();  // nothing of an earlier kernel is read or overwritten before this
     const unsigned px = blockIdx.x * TPX + lane;
     const bool live = px < (unsigned)g.n_px;
+    const int n_live = (int)min((unsigned)TPX, (unsigned)g.n_px - blockIdx.x * TPX);  // pixels of this block
     const unsigned n = live ? px / (unsigned)g.hw : 0u;
     const unsigned r = live ? px - n * (unsigned)g.hw : 0u;
     if (warp == 0) {
@@ -190,14 +198,15 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
     // Warp w owns the TPER consecutive channels [TPER w, TPER (w + 1)) of every chunk.
     const int cw = TPER * warp;  // first channel of this warp inside a chunk
     const float *pw = g.src + (long)n * g.img_stride + r + (long)cw * g.hw;
+    const unsigned pitch = (unsigned)g.hw * 4u;  // bytes between channels; the host checks the range
     float v[TPER];
     if (live && TCC <= g.ic) {
 #pragma unroll
-        for (int i = 0; i < TPER; i++) v[i] = ld_stream(pw + (long)i * g.hw);
+        for (int i = 0; i < TPER; i++) v[i] = ld_stream(row_ptr(pw, i, pitch));
     } else {
 #pragma unroll
         for (int i = 0; i < TPER; i++)
-            v[i] = (live && cw + i < g.ic) ? ld_stream(pw + (long)i * g.hw) : 0.f;
+            v[i] = (live && cw + i < g.ic) ? ld_stream(row_ptr(pw, i, pitch)) : 0.f;
     }
     for (int c0 = 0; c0 < c_end; c0 += TCC) {
         const bool full = c0 + TCC <= g.ic;  // no channel tail in this chunk
@@ -233,11 +242,11 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
             const float *pn = pw + (long)(c0 + TCC) * g.hw;
             if (live && c0 + 2 * TCC <= g.ic) {
 #pragma unroll
-                for (int i = 0; i < TPER; i++) v[i] = ld_stream(pn + (long)i * g.hw);
+                for (int i = 0; i < TPER; i++) v[i] = ld_stream(row_ptr(pn, i, pitch));
             } else {
 #pragma unroll
                 for (int i = 0; i < TPER; i++)
-                    v[i] = (live && c0 + TCC + cw + i < g.ic) ? ld_stream(pn + (long)i * g.hw) : 0.f;
+                    v[i] = (live && c0 + TCC + cw + i < g.ic) ? ld_stream(row_ptr(pn, i, pitch)) : 0.f;
             }
         }
         if (WITH_A && warp == 0) {
@@ -273,12 +282,10 @@ __global__ void __launch_bounds__(TWARPS * 32) binarize_bytes_nchw_kernel(const 
             constexpr int PPW = 32 / LPP;  // pixels a warp writes per pass
             const int sub = lane / LPP, wl = lane % LPP;
             if (sub < PPW && wl < n8) {
-                for (int pi = PPW * first + sub; pi < TPX; pi += PPW * step) {
-                    const long row = row_s[pi];
-                    if (row >= 0)
-                        reinterpret_cast<uint2 *>(g.out)[row + (c0 >> 3) + wl] =
-                            *reinterpret_cast<const uint2 *>(&b_s[pi * TLD + 8 * wl]);
-                }
+                uint2 *out = reinterpret_cast<uint2 *>(g.out) + (c0 >> 3) + wl;
+                const uint8_t *tile = b_s + 8 * wl;
+                for (int pi = PPW * first + sub; pi < n_live; pi += PPW * step)
+                    out[row_s[pi]] = *reinterpret_cast<const uint2 *>(tile + pi * TLD);
             }
         }
         __syncthreads();
@@ -336,7 +343,8 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
     const int threads = 128;
     const unsigned blocks = (unsigned)((g.n_px + threads - 1) / threads);
     if (blocks == 0) return cudaSuccess;
-    if (!p.src_nhwc && (p.family == kTcgen05 || !WITH_PACK) && g.n_px < (1L << 31) - TPX) {
+    if (!p.src_nhwc && (p.family == kTcgen05 || !WITH_PACK) && g.n_px < (1L << 31) - TPX &&
+        (long)p.ih * p.iw < (1L << 24)) {
         // Shared-memory carve-out sized for kResidentBlocks blocks per SM, once per device. Left
         // to itself the driver sizes it for as many blocks as the thread count allows, which
         // leaves the L1 too small for the loads in flight; a kernel that streams with 32 loads
