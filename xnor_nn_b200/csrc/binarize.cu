@@ -126,8 +126,8 @@ __global__ void __launch_bounds__(128) binarize_kernel(const BinArgs g) {
 // to a float tile and the sign byte to a byte tile in shared memory, both pixel-major. Warp 0 then
 // adds the float tile up channel by channel, one lane per pixel, which keeps upstream's summation
 // order, while the other warps copy the byte tile out, 8 bytes per lane, a pixel's 128-byte line
-// per half warp. Seven blocks are resident per SM (72 registers per thread, and the shared-memory
-// carve-out is sized to match).
+// per half warp. Five blocks are resident per SM (nine of the 96-channel kind): the shared-memory
+// carve-out is sized for that, see launch_bin().
 //
 // The kernel is as much bound by instruction issue as by memory (a profile of the first version
 // on the 96-channel AlexNet layer: 29 instructions issued per global load, the schedulers busy
@@ -336,7 +336,8 @@ BinArgs bin_args(const Plan &p, const float *src, void *out, float *a) {
     return g;
 }
 
-constexpr int kResidentBlocks = 7;  // tiled kernel: blocks per SM the carve-out is sized for
+// tiled kernels: blocks per SM the carve-out is sized for (chunks of 128 and of 96 channels)
+constexpr int kResidentBlocks = 5, kResidentBlocks96 = 9;
 
 template <bool WITH_A, bool WITH_PACK>
 cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
@@ -345,30 +346,30 @@ cudaError_t launch_bin(const Plan &p, const BinArgs &g, cudaStream_t s) {
     if (blocks == 0) return cudaSuccess;
     if (!p.src_nhwc && (p.family == kTcgen05 || !WITH_PACK) && g.n_px < (1L << 31) - TPX &&
         (long)p.ih * p.iw < (1L << 24)) {
-        // Shared-memory carve-out sized for kResidentBlocks blocks per SM, once per device. Left
+        // Shared-memory carve-out sized for a fixed number of blocks per SM, once per device. Left
         // to itself the driver sizes it for as many blocks as the thread count allows, which
-        // leaves the L1 too small for the loads in flight; a kernel that streams with 32 loads
-        // per thread outstanding does not need that many warps. Measured on conv4, minibatch 256:
-        // the pass with the mean-|x| map 20.9 -> 19.1 us, and the convolution that follows starts
-        // about 3 us earlier (whole step 65.5 -> 60.4 us).
+        // leaves the L1 too small: the loads in flight occupy it although they do not allocate
+        // lines to keep, and a kernel that streams with 32 loads per thread outstanding does not
+        // need that many warps. Measured on conv4, minibatch 256, pass with the mean-|x| map:
+        // eight blocks (an L1 of 32 KB) 20.4 us, seven or six (64 KB) 16.9-17.3, five (96 KB)
+        // 17.0-17.1 with the whole step 0.5 us shorter, four or three (128 KB) 18.1. The
+        // 96-channel kernel on conv2: nine of its blocks (the same 64 KB of L1) 9.3 us, seven
+        // (96 KB) 9.7, five 11.2.
         static std::atomic<bool> tuned[64];
         int dev = 0;
         cudaGetDevice(&dev);
         if (!tuned[dev & 63].exchange(true, std::memory_order_acq_rel)) {
-            const int blocks = kResidentBlocks;
-            cudaFuncAttributes fa;
             int smem_sm = 0;
-            if (blocks > 0 &&
-                cudaFuncGetAttributes(&fa, binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>) == cudaSuccess &&
-                cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess &&
-                smem_sm > 0) {
-                long pct = (100L * blocks * ((long)fa.sharedSizeBytes + 1024) + smem_sm - 1) / smem_sm;
+            cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+            auto carve = [&](auto kernel, int resident) {
+                cudaFuncAttributes fa;
+                if (smem_sm <= 0 || cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) return;
+                long pct = (100L * resident * ((long)fa.sharedSizeBytes + 1024) + smem_sm - 1) / smem_sm;
                 if (pct > 100) pct = 100;
-                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>,
-                                     cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
-                cudaFuncSetAttribute(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24>,
-                                     cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
-            }
+                cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)pct);
+            };
+            carve(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 32>, kResidentBlocks);
+            carve(binarize_bytes_nchw_kernel<WITH_A, WITH_PACK, 24>, kResidentBlocks96);
             (void)cudaGetLastError();
         }
         note_launch();
